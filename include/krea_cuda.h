@@ -1,0 +1,192 @@
+/*
+ * libkrea_cuda - C ABI of the B200 (sm_100a) implementation of the Krea 2 Turbo DiT joint text+image
+ * attention path: per-head QK-RMSNorm + RoPE prologue and flash attention with head_dim 128.
+ *
+ * The two operator entry points take the same arguments, in the same units (elements, not bytes) and
+ * with the same row layouts as the reference engine's operator API, so a caller of
+ *     Metal::qk_norm_rope   (engine/src/metal.h:80-82,  engine/src/metal.mm:182-191)
+ *     Metal::attention      (engine/src/metal.h:83-88,  engine/src/metal.mm:193-202)
+ * can switch to them by replacing its buffers with CUDA device pointers.  Conventions follow the
+ * reference's only C ABI (engine/src/krea.h): opaque handle, plain structs, `char* err, int errlen`
+ * at creation, integer status returns, no exceptions across the boundary.
+ *
+ * Execution model: every call validates its arguments on the host, then enqueues kernels on the
+ * handle's CUDA stream and returns without synchronising (the reference's operators likewise only
+ * encode into the current command buffer, engine/src/metal.mm:130-135).  One caller per handle at a
+ * time, like the reference (ui/krea.py:140,223 holds a lock around each engine call).  There is no CPU
+ * fallback: without a CUDA device krea_cuda_create fails.
+ *
+ * Pointer alignment: every tensor pointer and every row start must be 16-byte aligned (ld, column
+ * offsets and batch strides multiples of 8 bf16 elements) - the reference's kernels make the same
+ * assumption with their 16-byte vector loads (engine/kernels/attention.metal:102).
+ */
+#ifndef KREA_CUDA_H
+#define KREA_CUDA_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KREA_CUDA_API __attribute__((visibility("default")))
+#else
+#define KREA_CUDA_API
+#endif
+
+typedef struct krea_cuda krea_cuda;
+
+/* Status codes.  0 = ok, negative = error (the reference's C ABI returns -1 on error, krea.h:66-69). */
+enum {
+  KREA_CUDA_OK = 0,
+  KREA_CUDA_E_ARG = -1,         /* invalid argument; nothing was launched */
+  KREA_CUDA_E_UNSUPPORTED = -2, /* valid in the reference's API but not built here; nothing was launched */
+  KREA_CUDA_E_CUDA = -3,        /* a CUDA runtime / driver call failed */
+  KREA_CUDA_E_DEVICE = -4,      /* a kernel gave up on a bounded wait and reported it (see krea_cuda_sync) */
+  KREA_CUDA_E_NOMEM = -5        /* workspace allocation failed or caller-provided scratch too small */
+};
+
+/* RoPE modes of qk_norm_rope: enum RopeMode, engine/src/metal.h:44; engine/kernels/norm.metal:64-66. */
+enum { KREA_CUDA_ROPE_PAIRS = 0, KREA_CUDA_ROPE_HALF = 1, KREA_CUDA_ROPE_NONE = 2 };
+
+/* ---- lifetime (pattern of krea_create / krea_destroy, engine/src/krea.h:54-55) ---- */
+KREA_CUDA_API krea_cuda* krea_cuda_create(int device, char* err, int errlen);
+KREA_CUDA_API void krea_cuda_destroy(krea_cuda* h);
+/* Message of the last failing call on this handle ("" if none). */
+KREA_CUDA_API const char* krea_cuda_last_error(krea_cuda* h);
+/* Use the caller's cudaStream_t (NULL = the handle's own stream, created by krea_cuda_create). */
+KREA_CUDA_API int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream);
+/* Wait for the stream (the counterpart of Metal::wait, engine/src/metal.h:57-58) and return
+ * KREA_CUDA_E_DEVICE if any kernel since the last sync reported a timed-out wait. */
+KREA_CUDA_API int krea_cuda_sync(krea_cuda* h);
+/* Number of kernels this handle has launched so far. */
+KREA_CUDA_API uint64_t krea_cuda_launch_count(krea_cuda* h);
+
+/* ---- Metal::qk_norm_rope (engine/src/metal.h:80-82; kernel engine/kernels/norm.metal:81-134) ----
+ * In place on bf16 rows [rows, ld]: for every row and head, x <- bf16(rope(x * rsqrt(mean(x^2) + eps) * w)).
+ * q heads at column q_off + h*128 (n_q of them, weight wq), k heads at k_off + h*128 (n_k, weight wk);
+ * n_q or n_k may be 0.  cos/sin: f32 [rows, 64] per-row tables (ignored for KREA_CUDA_ROPE_NONE).
+ * big_dim >= 0: that channel's value goes to qbig [rows, n_q] / kbig [rows, n_k] (fp32) and is stored as 0. */
+typedef struct {
+  void* qkv;
+  const float* wq;
+  const float* wk;
+  const float* cos;
+  const float* sin;
+  int rows, ld;
+  int q_off, n_q;
+  int k_off, n_k;
+  float eps;
+  int rope_mode;
+  int big_dim; /* -1 = none */
+  float* qbig;
+  float* kbig;
+} krea_cuda_qknorm_args;
+KREA_CUDA_API int krea_cuda_qk_norm_rope(krea_cuda* h, const krea_cuda_qknorm_args* a);
+
+/* ---- Metal::attention (engine/src/metal.h:83-88; kernel engine/kernels/attention.metal:131-351) ----
+ * O[q, h*128 + d] = sum_k softmax_k(Q[q,h] . K[k,h/group] / sqrt(128)) V[k, h/group, d]  (x sigmoid(G) if G).
+ * Q [Lq, ldq], K [Lk, ldk], V [Lk, ldv], O [Lq, ldo], G [Lq, ldg]: bf16, head h at column h*128 (K/V: (h/group)*128).
+ * Operands are used as they are (Q and K already normalised and rotated).  fp32 scores, softmax and
+ * accumulation; P is rounded to bf16 for the PV product, the row sum stays fp32; a row without any
+ * visible key gives zeros.  QB [Lq, heads] / KB [Lk, heads/group]: optional fp32 rank-1 score term.
+ * Extensions beyond the reference (all-zero = reference behaviour): a batch dimension with per-tensor
+ * batch strides, and a text key-padding mask (see krea_cuda_joint_args). */
+typedef struct {
+  const void* Q;
+  const void* K;
+  const void* V;
+  void* O;
+  int Lq, Lk, heads;
+  int ldq, ldk, ldv, ldo;
+  int group;
+  int causal;
+  int q_pos0;
+  const void* G;
+  int ldg;
+  const float* QB;
+  const float* KB;
+  /* extensions */
+  int batch;                  /* 0 or 1 = single sample */
+  int64_t bsq, bsk, bsv, bso, bsg; /* batch strides in elements */
+  const int32_t* text_len;    /* device pointer, int32 [batch], or NULL */
+  int text_slots;
+  int q_row0;                 /* sequence position of query row 0 (for the padding test of query rows) */
+} krea_cuda_attn_args;
+KREA_CUDA_API int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a);
+
+/* ---- The whole path in one call: DiT::qk_rope + DiT::attend (engine/src/model.mm:271-288) ----
+ * Q, K, V are the raw projections (e.g. column blocks of one fused q|k|v row buffer).  Neither input is
+ * modified: Q is normalised and rotated inside the attention kernel as it is staged; K is normalised
+ * and rotated once into scratch memory by a pre-pass.  Query row i sits at sequence position
+ * q_row0 + i (the reference's row0, model.mm:271-288); key row j at position j; cos/sin: f32 [>= max(q_row0+Lq, Lk), 64].
+ * text_len (device, int32 [batch]) with text_slots > 0: keys at positions [text_len[b], text_slots) are
+ * padding and contribute nothing; query rows at those positions are written as zeros.
+ * k_scratch: caller-owned device scratch of k_scratch_bytes >= krea_cuda_joint_scratch_bytes(a), or
+ * NULL to let the handle allocate (and keep, growing on demand) its own. */
+typedef struct {
+  const void* Q;
+  const void* K;
+  const void* V;
+  void* O;
+  int batch;
+  int Lq, Lk, q_row0;
+  int heads, group;
+  int ldq, ldk, ldv, ldo;
+  int64_t bsq, bsk, bsv, bso;
+  const float* wq;
+  const float* wk;
+  const float* cos;
+  const float* sin;
+  float eps;
+  int rope_mode;
+  const int32_t* text_len;
+  int text_slots;
+  const void* G;
+  int ldg;
+  int64_t bsg;
+  void* k_scratch;
+  size_t k_scratch_bytes;
+} krea_cuda_joint_args;
+KREA_CUDA_API size_t krea_cuda_joint_scratch_bytes(const krea_cuda_joint_args* a);
+KREA_CUDA_API int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_args* a);
+
+/* Same call with every pointer in HOST memory (the reference's Tensor is CPU-visible unified memory,
+ * engine/src/metal.h:14-23): copies the operands to device buffers owned by the handle, runs
+ * krea_cuda_joint_attention, copies O back and synchronises.  Pinned host memory makes the copies
+ * asynchronous DMA; pageable memory works too.  k_scratch is ignored. */
+KREA_CUDA_API int krea_cuda_joint_attention_host(krea_cuda* h, const krea_cuda_joint_args* a);
+
+/* ---- RoPE tables, built on the host like DiT::set_grid (engine/src/model.mm:290-315) ----
+ * cos/sin: host f32 [T + gh*gw, 64]; text rows (the first T) sit at position 0.
+ * ref3axis: the reference model's split (pairs 0-15 frame = 0, 16-39 grid row, 40-63 grid column, theta 1000).
+ * axial2d: two axes of 32 pairs (row, then column), frequency k = theta^(-2k/64). */
+KREA_CUDA_API int krea_cuda_rope_tables_ref3axis(float* cos, float* sin, int T, int gh, int gw);
+KREA_CUDA_API int krea_cuda_rope_tables_axial2d(float* cos, float* sin, int T, int gh, int gw, double theta);
+
+/* ---- sequence-parallel resharding helpers (no counterpart in the reference, which is single-device) ----
+ * Pack / unpack kernels either side of an all-to-all that turns sequence-sharded rows (all heads, rows
+ * [r*S/P, (r+1)*S/P)) into head-sharded rows (all S rows, heads [r*H/P, (r+1)*H/P)) and back.
+ *   pack:   dst[peer][row][c] = src[row][src_col0 + peer*cols_per_rank + c]     (one block per destination)
+ *   unpack: dst[row][dst_col0 + peer*cols_per_rank + c] = src[peer][row][c]     (the inverse)
+ * Forward: pack the local rows by destination head block, all-to-all; the received blocks, in peer
+ * order, already are the S rows of the local heads.  Backward: send the output rows as they are
+ * (row blocks are contiguous), all-to-all, unpack merges the per-peer head blocks into full rows.
+ * bf16 elements; cols_per_rank, the leading dimensions and column offsets are multiples of 8. */
+typedef struct {
+  const void* src;
+  void* dst;
+  int nranks;
+  int rows;          /* rows held locally */
+  int cols_per_rank; /* bf16 elements per row per peer */
+  int src_ld, dst_ld;
+  int src_col0, dst_col0;
+} krea_cuda_reshard_args;
+KREA_CUDA_API int krea_cuda_reshard_pack(krea_cuda* h, const krea_cuda_reshard_args* a);
+KREA_CUDA_API int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,93 @@
+"""ctypes binding of libkrea_cuda (include/krea_cuda.h), in the style of the reference's own binding of
+its C ABI (ui/krea.py:120-145): load the shared object, declare argtypes/restypes, mirror the structs.
+
+The library is looked up in-tree (krea_image_b200/_build); if it is missing this module raises - there
+is no fallback implementation.
+"""
+import ctypes
+import os
+
+from . import build as _build
+
+OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM = 0, -1, -2, -3, -4, -5
+ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
+
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+_i64 = ctypes.c_int64
+
+
+class QKNormArgs(ctypes.Structure):
+    _fields_ = [("qkv", _vp), ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp),
+                ("rows", _int), ("ld", _int), ("q_off", _int), ("n_q", _int), ("k_off", _int), ("n_k", _int),
+                ("eps", ctypes.c_float), ("rope_mode", _int), ("big_dim", _int), ("qbig", _vp), ("kbig", _vp)]
+
+
+class AttnArgs(ctypes.Structure):
+    _fields_ = [("Q", _vp), ("K", _vp), ("V", _vp), ("O", _vp),
+                ("Lq", _int), ("Lk", _int), ("heads", _int),
+                ("ldq", _int), ("ldk", _int), ("ldv", _int), ("ldo", _int),
+                ("group", _int), ("causal", _int), ("q_pos0", _int),
+                ("G", _vp), ("ldg", _int), ("QB", _vp), ("KB", _vp),
+                ("batch", _int), ("bsq", _i64), ("bsk", _i64), ("bsv", _i64), ("bso", _i64), ("bsg", _i64),
+                ("text_len", _vp), ("text_slots", _int), ("q_row0", _int)]
+
+
+class JointArgs(ctypes.Structure):
+    _fields_ = [("Q", _vp), ("K", _vp), ("V", _vp), ("O", _vp),
+                ("batch", _int), ("Lq", _int), ("Lk", _int), ("q_row0", _int), ("heads", _int), ("group", _int),
+                ("ldq", _int), ("ldk", _int), ("ldv", _int), ("ldo", _int),
+                ("bsq", _i64), ("bsk", _i64), ("bsv", _i64), ("bso", _i64),
+                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("eps", ctypes.c_float), ("rope_mode", _int),
+                ("text_len", _vp), ("text_slots", _int), ("G", _vp), ("ldg", _int), ("bsg", _i64),
+                ("k_scratch", _vp), ("k_scratch_bytes", ctypes.c_size_t)]
+
+
+class ReshardArgs(ctypes.Structure):
+    _fields_ = [("src", _vp), ("dst", _vp), ("nranks", _int), ("rows", _int), ("cols_per_rank", _int),
+                ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
+
+
+# every symbol include/krea_cuda.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "krea_cuda_create": (_vp, [_int, ctypes.c_char_p, _int]),
+    "krea_cuda_destroy": (None, [_vp]),
+    "krea_cuda_last_error": (ctypes.c_char_p, [_vp]),
+    "krea_cuda_set_stream": (_int, [_vp, _vp]),
+    "krea_cuda_sync": (_int, [_vp]),
+    "krea_cuda_launch_count": (ctypes.c_uint64, [_vp]),
+    "krea_cuda_qk_norm_rope": (_int, [_vp, ctypes.POINTER(QKNormArgs)]),
+    "krea_cuda_attention": (_int, [_vp, ctypes.POINTER(AttnArgs)]),
+    "krea_cuda_joint_scratch_bytes": (ctypes.c_size_t, [ctypes.POINTER(JointArgs)]),
+    "krea_cuda_joint_attention": (_int, [_vp, ctypes.POINTER(JointArgs)]),
+    "krea_cuda_joint_attention_host": (_int, [_vp, ctypes.POINTER(JointArgs)]),
+    "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
+    "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
+    "krea_cuda_reshard_pack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
+    "krea_cuda_reshard_unpack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
+}
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.LIB
+
+
+def load(build_if_missing: bool = True) -> ctypes.CDLL:
+    """Load libkrea_cuda.so and declare every prototype.  Raises if the library cannot be found or built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path):
+        if not build_if_missing:
+            raise FileNotFoundError(f"{path} is missing: run `python -m krea_image_b200.build`")
+        _build.build()
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)   # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

@@ -1,0 +1,445 @@
+// Joint text+image flash attention for B200 (sm_100a), head_dim 128, bf16 in/out.
+//
+// Math and semantics follow the reference kernel engine/kernels/attention.metal:131-333 (scores and
+// softmax in fp32, P rounded to bf16 for the PV product while the row sum stays fp32, lazily updated
+// running max with a threshold of 8 in log2 units, empty rows give zeros, optional sigmoid gate fused
+// into the bf16 store) and, for the fused Q prologue, engine/kernels/norm.metal:81-134.  The
+// implementation shares nothing with it:
+//
+//   * one CTA = NQ tiles of 128 query rows of one (sample, head); S = Q K^T and O += P V run on the
+//     tcgen05 tensor cores with both accumulators in tensor memory (TMEM), issued by a single thread;
+//   * K and V tiles (128 keys x 128) are fetched by TMA into a ring of 128B-swizzled shared-memory
+//     stages by one producer warp; mbarriers carry every hand-off;
+//   * each of the 128 threads of a softmax warpgroup owns one query row (= one TMEM lane), so row max
+//     and row sum need no shuffles; P is written back to TMEM (aliasing S) as the A operand of P V;
+//   * Q rows are loaded once with 16-byte loads, optionally RMS-normalised and rotated (fp32), rounded
+//     to bf16 and stored in the swizzled layout the MMA wants - the Q half of the prologue costs no
+//     extra pass over memory;
+//   * every wait is bounded: on a timeout the CTA records a code in a status word and runs to its
+//     normal exit (TMEM released), so a logic error can never hang the GPU.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "attention_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace krea {
+
+constexpr int D = 128;               // head_dim
+constexpr int BM = 128;              // query rows per tile (= TMEM lanes)
+constexpr int BN = 128;              // keys per tile
+constexpr int TILE_BYTES = BN * D * 2;       // 32 KB: one K or V tile, or one Q tile
+constexpr int HALF_BYTES = TILE_BYTES / 2;   // two 64-column halves, each 128 rows x 128 B
+constexpr int NSTAGE = 4;            // K/V ring depth (K_j and V_j take one stage each)
+constexpr float LAZY_TH = 8.0f;      // attention.metal:33-36
+
+// wait sites (reported in the status word)
+enum : uint32_t { SITE_Q = 1, SITE_KV_FULL = 2, SITE_KV_EMPTY = 3, SITE_S = 4, SITE_P = 5, SITE_PV = 6, SITE_DRAIN = 7 };
+
+template <int NQ>
+struct SmemLayout {
+  static constexpr int q_off = 0;
+  static constexpr int kv_off = NQ * TILE_BYTES;
+  static constexpr int bar_off = kv_off + NSTAGE * TILE_BYTES;
+  // barriers: q_ready[NQ], s_full[NQ], p_full[NQ], pv_done[NQ], kv_full[NSTAGE], kv_empty[NSTAGE]
+  static constexpr int n_bars = 4 * NQ + 2 * NSTAGE;
+  static constexpr int misc_off = bar_off + n_bars * 8;
+  static constexpr int total = misc_off + 16;
+};
+
+// First / one-past-last fully masked key tile for padding range [lo, hi).
+__device__ __forceinline__ void skip_range(int lo, int hi, int& first, int& end) {
+  first = (lo + BN - 1) / BN;
+  end = hi / BN;
+  if (end < first) end = first;
+}
+
+template <int NQ>
+__global__ void __launch_bounds__(NQ * 128 + 64, 1)
+attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle needs
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  using L = SmemLayout<NQ>;
+  uint8_t* q_smem = smem + L::q_off;
+  uint8_t* kv_smem = smem + L::kv_off;
+  uint64_t* bars = (uint64_t*)(smem + L::bar_off);
+  uint64_t* q_ready = bars;
+  uint64_t* s_full = bars + NQ;
+  uint64_t* p_full = bars + 2 * NQ;
+  uint64_t* pv_done = bars + 3 * NQ;
+  uint64_t* kv_full = bars + 4 * NQ;
+  uint64_t* kv_empty = kv_full + NSTAGE;
+  uint32_t* tmem_slot = (uint32_t*)(smem + L::misc_off);
+  volatile uint32_t* abort_word = (volatile uint32_t*)(smem + L::misc_off + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / p.group;
+  const int q0 = qblk * (NQ * BM);
+
+  // key tiles: all tiles of [0, Lk) except those lying entirely inside the padding range
+  int pad_lo = 0, pad_hi = 0;
+  if (p.text_len != nullptr) {
+    pad_lo = min(max(p.text_len[b], 0), p.text_slots);
+    pad_hi = p.text_slots;
+  }
+  int skip_first, skip_end;
+  skip_range(pad_lo, pad_hi, skip_first, skip_end);
+  const int nkt_all = (p.Lk + BN - 1) / BN;
+  skip_first = min(skip_first, nkt_all);
+  skip_end = min(skip_end, nkt_all);
+  const int n_tiles = nkt_all - (skip_end - skip_first);
+  auto tile_of = [&](int j) { return j < skip_first ? j : j + (skip_end - skip_first); };
+
+  constexpr uint32_t TMEM_COLS = NQ * 256;
+  if (threadIdx.x == 0) {
+    for (int g = 0; g < NQ; g++) {
+      mbar_init(&q_ready[g], 128);
+      mbar_init(&s_full[g], 1);
+      mbar_init(&p_full[g], 128);
+      mbar_init(&pv_done[g], 1);
+    }
+    for (int s = 0; s < NSTAGE; s++) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    abort_word[0] = (p.status != nullptr && *p.status != 0u) ? 0xFFu : 0u;  // a failed launch poisons later CTAs
+    abort_word[1] = 0u;                                                     // private word of the drain loop
+    fence_mbar_init();
+  }
+  if (warp == NQ * 4 + 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < NQ * 4) {
+    // =============================== softmax / epilogue warpgroups ===============================
+    const int g = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
+    const int row = q0 + g * BM + r;
+    const bool tile_active = (q0 + g * BM) < p.Lq;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t tS = lane_addr + (uint32_t)(g * BN);
+    const uint32_t tO = lane_addr + (uint32_t)(NQ * BN + g * D);
+
+    if (tile_active && n_tiles > 0) {
+      // ---- stage Q (with the fused RMSNorm + RoPE prologue when weights are given) ----
+      {
+        const int rc = min(row, p.Lq - 1);               // rows past Lq are clamped, never stored
+        const uint4* src = (const uint4*)(p.Q + (size_t)b * p.bsq + (size_t)rc * p.ldq + (size_t)h * D);
+        uint4 raw[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++) raw[c] = __ldg(src + c);
+        uint8_t* qdst = q_smem + g * TILE_BYTES + r * 128;
+        if (p.wq != nullptr) {
+          float ss = 0.f;
+#pragma unroll
+          for (int c = 0; c < 16; c++) {
+            const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              const float a = bf16lo_to_f32(w4[e]), bb = bf16hi_to_f32(w4[e]);
+              ss = fmaf(a, a, ss);
+              ss = fmaf(bb, bb, ss);
+            }
+          }
+          const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
+          const int pos = p.q_row0 + rc;
+          const float4* cr = (const float4*)(p.cos + (size_t)pos * 64);
+          const float4* sr = (const float4*)(p.sin + (size_t)pos * 64);
+          const float4* wv = (const float4*)p.wq;
+          if (p.rope_mode == 1) {
+            // rotate-half: channel i pairs with i + 64 (norm.metal:114-126); chunk c pairs with chunk c + 8
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+              const uint32_t lo4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+              const uint32_t hi4[4] = {raw[c + 8].x, raw[c + 8].y, raw[c + 8].z, raw[c + 8].w};
+              float xl[8], xh[8], cs[8], sn[8];
+              const float4 wl0 = __ldg(wv + 2 * c), wl1 = __ldg(wv + 2 * c + 1);
+              const float4 wh0 = __ldg(wv + 16 + 2 * c), wh1 = __ldg(wv + 16 + 2 * c + 1);
+              const float wl[8] = {wl0.x, wl0.y, wl0.z, wl0.w, wl1.x, wl1.y, wl1.z, wl1.w};
+              const float wh[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
+              const float4 c0 = __ldg(cr + 2 * c), c1 = __ldg(cr + 2 * c + 1), s0 = __ldg(sr + 2 * c), s1 = __ldg(sr + 2 * c + 1);
+              const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+              const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                xl[2 * e] = bf16lo_to_f32(lo4[e]) * rrms * wl[2 * e];
+                xl[2 * e + 1] = bf16hi_to_f32(lo4[e]) * rrms * wl[2 * e + 1];
+                xh[2 * e] = bf16lo_to_f32(hi4[e]) * rrms * wh[2 * e];
+                xh[2 * e + 1] = bf16hi_to_f32(hi4[e]) * rrms * wh[2 * e + 1];
+              }
+#pragma unroll
+              for (int e = 0; e < 8; e++) {
+                cs[e] = xl[e] * cc[e] - xh[e] * sc[e];
+                sn[e] = xh[e] * cc[e] + xl[e] * sc[e];
+              }
+              raw[c] = make_uint4(pack_bf16x2(cs[0], cs[1]), pack_bf16x2(cs[2], cs[3]), pack_bf16x2(cs[4], cs[5]), pack_bf16x2(cs[6], cs[7]));
+              raw[c + 8] = make_uint4(pack_bf16x2(sn[0], sn[1]), pack_bf16x2(sn[2], sn[3]), pack_bf16x2(sn[4], sn[5]), pack_bf16x2(sn[6], sn[7]));
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; c++) {
+              const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+              const float4 wa = __ldg(wv + 2 * c), wb = __ldg(wv + 2 * c + 1);
+              const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+              float4 cc = make_float4(1.f, 1.f, 1.f, 1.f), sc = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.rope_mode == 0) {  // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113)
+                cc = __ldg(cr + c);
+                sc = __ldg(sr + c);
+              }
+              const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
+              uint32_t o4[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                const float x0 = bf16lo_to_f32(w4[e]) * rrms * ww[2 * e];
+                const float x1 = bf16hi_to_f32(w4[e]) * rrms * ww[2 * e + 1];
+                o4[e] = pack_bf16x2(x0 * cf[e] - x1 * sf[e], x0 * sf[e] + x1 * cf[e]);
+              }
+              raw[c] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            }
+          }
+        }
+        // 128-byte swizzle: 16-byte chunk c of row r lands in chunk slot c ^ (r & 7) of its 128 B row
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+          uint8_t* dst = qdst + (c >> 3) * HALF_BYTES + (((c & 7) ^ (r & 7)) << 4);
+          *(uint4*)dst = raw[c];
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&q_ready[g]);
+      }
+
+      // ---- online softmax over the key tiles ----
+      float m_i = -INFINITY;   // running max, log2 units (scaled scores)
+      float l_i = 0.f;         // running row sum of exp2(s - m_i), fp32
+      const float sc2 = p.scale_log2;
+      for (int j = 0; j < n_tiles; j++) {
+        const int kt = tile_of(j);
+        const int key0 = kt * BN;
+        mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
+        tc_fence_after();
+        uint32_t sv[128];
+        tmem_ld32(tS + 0, sv + 0);
+        tmem_ld32(tS + 32, sv + 32);
+        tmem_ld32(tS + 64, sv + 64);
+        tmem_ld32(tS + 96, sv + 96);
+        tmem_wait_ld();
+        float* s = (float*)sv;
+        const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 128; c++) {
+            const int key = key0 + c;
+            const bool ok = key < p.Lk && !(key >= pad_lo && key < pad_hi);
+            s[c] = ok ? s[c] : -INFINITY;
+          }
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int c = 1; c < 128; c++) mx = fmaxf(mx, s[c]);
+        const float lm = mx * sc2;
+        const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_new = need ? lm : m_i;
+          const float alpha = (m_i == -INFINITY) ? 0.f : ex2_approx(m_i - m_new);
+          m_i = m_new;
+          l_i *= alpha;
+          if (j > 0) {
+            // rescale this row of O; P V of the previous tile must have landed first
+            mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ov[32];
+              tmem_ld32(tO + c0, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+              tmem_st32(tO + c0, ov);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
+        uint32_t pk[64];
+        float lsum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 128; c += 2) {
+          const float p0 = ex2_approx(fmaf(s[c], sc2, -m_use));
+          const float p1 = ex2_approx(fmaf(s[c + 1], sc2, -m_use));
+          lsum += p0 + p1;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        l_i += lsum;
+        tmem_st32(tS + 0, pk);
+        tmem_st32(tS + 32, pk + 32);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&p_full[g]);
+      }
+
+      // ---- epilogue: O / l (x sigmoid(G)) -> bf16 ----
+      mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV);
+      tc_fence_after();
+      const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
+      const int pos = p.q_row0 + row;
+      const bool padded_row = pos >= pad_lo && pos < pad_hi;
+      const bool store_row = row < p.Lq;
+      const int rs = store_row ? row : 0;
+      uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)rs * p.ldo + (size_t)h * D);
+      const uint4* gsrc = p.G ? (const uint4*)(p.G + (size_t)b * p.bsg + (size_t)rs * p.ldg + (size_t)h * D) : nullptr;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t ov[32];
+        tmem_ld32(tO + c0, ov);   // .sync.aligned: executed by the whole warp, stores are predicated below
+        tmem_wait_ld();
+        if (store_row) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) f[e] = padded_row ? 0.f : __uint_as_float(ov[q4 * 8 + e]) * inv;
+            if (gsrc) {
+              const uint4 gv = __ldg(gsrc + (c0 >> 3) + q4);
+              const uint32_t g4[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                f[2 * e] *= 1.0f / (1.0f + __expf(-bf16lo_to_f32(g4[e])));
+                f[2 * e + 1] *= 1.0f / (1.0f + __expf(-bf16hi_to_f32(g4[e])));
+              }
+            }
+            dst[(c0 >> 3) + q4] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+          }
+        }
+      }
+    } else if (tile_active && row < p.Lq) {
+      // no visible key at all: zeros
+      uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)row * p.ldo + (size_t)h * D);
+#pragma unroll
+      for (int c = 0; c < 16; c++) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  } else if (warp == NQ * 4) {
+    // ======================================= TMA producer =======================================
+    if (lane == 0 && n_tiles > 0) {
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      int issued = 0;
+      for (int j = 0; j < n_tiles; j++) {
+        const int key0 = tile_of(j) * BN;
+        for (int kv = 0; kv < 2; kv++) {
+          const int n = 2 * j + kv, stage = n % NSTAGE;
+          const bool ok = mbar_wait(&kv_empty[stage], ((n / NSTAGE) & 1) ^ 1, abort_word, SITE_KV_EMPTY);
+          if (!ok) break;
+          uint8_t* dst = kv_smem + stage * TILE_BYTES;
+          mbar_arrive_expect_tx(&kv_full[stage], TILE_BYTES);
+          const CUtensorMap* tm = kv == 0 ? &tmK : &tmV;
+          tma_load_3d(dst, tm, &kv_full[stage], kvh * D, key0, b);
+          tma_load_3d(dst + HALF_BYTES, tm, &kv_full[stage], kvh * D + 64, key0, b);
+          issued = n + 1;
+        }
+        if (*abort_word != 0u) break;
+      }
+      if (*abort_word != 0u) {
+        // make sure no copy is still in flight into this CTA's shared memory when it exits
+        for (int n = max(issued - NSTAGE, 0); n < issued; n++)
+          mbar_wait_slow(&kv_full[n % NSTAGE], (n / NSTAGE) & 1, abort_word + 1, SITE_DRAIN);
+      }
+    }
+  } else {
+    // ======================================== MMA issuer ========================================
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, true);
+      bool active[NQ];
+      for (int g = 0; g < NQ; g++) active[g] = (q0 + g * BM) < p.Lq;
+      const uint32_t q_base = smem_u32(q_smem), kv_base = smem_u32(kv_smem);
+
+      auto issue_qk = [&](int g, int stage) {
+        const uint32_t qa = q_base + g * TILE_BYTES, kb = kv_base + stage * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+          umma_ss(tmem_base + g * BN, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(kb + off, 16, 1024), idesc_qk, k > 0);
+        }
+        umma_commit(&s_full[g]);
+      };
+      auto issue_pv = [&](int g, int stage, bool first) {
+        const uint32_t vb = kv_base + stage * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          // 16 keys per MMA: A = 8 packed-bf16 columns of P in TMEM, B = 16 rows (2048 B) of the V stage
+          umma_ts(tmem_base + NQ * BN + g * D, tmem_base + g * BN + k * 8, umma_smem_desc(vb + k * 2048, HALF_BYTES, 1024), idesc_pv,
+                  (!first || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&pv_done[g]);
+      };
+
+      for (int g = 0; g < NQ; g++)
+        if (active[g]) mbar_wait(&q_ready[g], 0, abort_word, SITE_Q);
+      mbar_wait(&kv_full[0], 0, abort_word, SITE_KV_FULL);   // K_0
+      tc_fence_after();
+      for (int g = 0; g < NQ; g++)
+        if (active[g]) issue_qk(g, 0);
+      umma_commit(&kv_empty[0]);
+
+      for (int j = 0; j < n_tiles; j++) {
+        const int nv = 2 * j + 1, nk = 2 * j + 2;
+        const bool has_next = j + 1 < n_tiles;
+        mbar_wait(&kv_full[nv % NSTAGE], (nv / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        if (has_next) mbar_wait(&kv_full[nk % NSTAGE], (nk / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        for (int g = 0; g < NQ; g++) {
+          if (!active[g]) continue;
+          mbar_wait(&p_full[g], j & 1, abort_word, SITE_P);
+          tc_fence_after();
+          issue_pv(g, nv % NSTAGE, j == 0);
+          if (has_next) issue_qk(g, nk % NSTAGE);
+        }
+        umma_commit(&kv_empty[nv % NSTAGE]);
+        if (has_next) umma_commit(&kv_empty[nk % NSTAGE]);
+        if (*abort_word != 0u) break;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == NQ * 4 + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && p.status != nullptr) {
+    const uint32_t a = *abort_word;
+    if (a != 0u && a != 0xFFu) atomicCAS(p.status, 0u, a | ((uint32_t)blockIdx.x << 8) | ((uint32_t)blockIdx.y << 20));
+  }
+}
+
+template <int NQ>
+static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, cudaStream_t stream) {
+  const int smem = SmemLayout<NQ>::total + 1024;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  dim3 grid((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
+  attn_fwd_sm100<NQ><<<grid, NQ * 128 + 64, smem, stream>>>(tmK, tmV, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int nq, cudaStream_t stream) {
+  return nq == 1 ? launch_impl<1>(tmK, tmV, p, stream) : launch_impl<2>(tmK, tmV, p, stream);
+}
+
+}  // namespace krea

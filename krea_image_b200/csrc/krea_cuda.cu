@@ -1,0 +1,511 @@
+// libkrea_cuda: the C ABI declared in include/krea_cuda.h.  Host side only: argument validation (so a bad
+// call can never reach the GPU), tensor-map construction, stream handling, error strings.  The entry
+// points mirror the reference's operator dispatch (engine/src/metal.mm:182-202) and its C ABI
+// conventions (engine/src/pipeline.mm:594-630: catch everything, return a status, copy a message).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+
+#include "../../include/krea_cuda.h"
+#include "attention_sm100.h"
+
+using namespace krea;
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct krea_cuda {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  uint32_t* status_dev = nullptr;   // kernels report timed-out waits here
+  uint32_t* status_host = nullptr;  // pinned mirror
+  void* ws = nullptr;               // scratch for the normalised K of the joint call
+  size_t ws_bytes = 0;
+  void* stage[8] = {};              // device copies for the host-pointer entry point
+  size_t stage_bytes[8] = {};
+  uint64_t launches = 0;
+  PFN_encodeTiled encode = nullptr;
+  int nq = 2;                       // query tiles per CTA
+};
+
+static int fail(krea_cuda* h, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (h) h->err = buf;
+  return code;
+}
+#define CUDA_TRY(h, expr)                                                                       \
+  do {                                                                                          \
+    cudaError_t e_ = (expr);                                                                    \
+    if (e_ != cudaSuccess) return fail(h, KREA_CUDA_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+extern "C" {
+
+krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
+  auto say = [&](const char* m, const char* d) {
+    if (err && errlen > 0) snprintf(err, (size_t)errlen, "%s%s", m, d ? d : "");
+  };
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n <= 0) {
+    say("krea_cuda_create: no CUDA device: ", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (device < 0 || device >= n) {
+    say("krea_cuda_create: device index out of range", nullptr);
+    return nullptr;
+  }
+  cudaDeviceProp prop;
+  if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
+    say("krea_cuda_create: ", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (prop.major != 10) {
+    say("krea_cuda_create: this library contains sm_100a code only (Blackwell B200 required)", nullptr);
+    return nullptr;
+  }
+  krea_cuda* h = new krea_cuda();
+  h->device = device;
+  bool ok = cudaSetDevice(device) == cudaSuccess;
+  ok = ok && cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) == cudaSuccess;
+  ok = ok && cudaMalloc((void**)&h->status_dev, 256) == cudaSuccess;
+  ok = ok && cudaMemset(h->status_dev, 0, 256) == cudaSuccess;
+  ok = ok && cudaMallocHost((void**)&h->status_host, 256) == cudaSuccess;
+  if (ok) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    ok = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && fn != nullptr;
+    h->encode = (PFN_encodeTiled)fn;
+  }
+  if (!ok) {
+    say("krea_cuda_create: CUDA initialisation failed: ", cudaGetErrorString(cudaGetLastError()));
+    krea_cuda_destroy(h);
+    return nullptr;
+  }
+  h->stream = h->own_stream;
+  if (const char* s = getenv("KREA_CUDA_NQ")) {  // debugging knob: 1 or 2 query tiles per CTA
+    const int v = atoi(s);
+    if (v == 1 || v == 2) h->nq = v;
+  }
+  return h;
+}
+
+void krea_cuda_destroy(krea_cuda* h) {
+  if (!h) return;
+  cudaSetDevice(h->device);
+  if (h->own_stream) cudaStreamSynchronize(h->own_stream);
+  if (h->status_dev) cudaFree(h->status_dev);
+  if (h->status_host) cudaFreeHost(h->status_host);
+  if (h->ws) cudaFree(h->ws);
+  for (int i = 0; i < 8; i++)
+    if (h->stage[i]) cudaFree(h->stage[i]);
+  if (h->own_stream) cudaStreamDestroy(h->own_stream);
+  delete h;
+}
+
+const char* krea_cuda_last_error(krea_cuda* h) { return h ? h->err.c_str() : "null handle"; }
+
+int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream) {
+  if (!h) return KREA_CUDA_E_ARG;
+  h->stream = cuda_stream ? (cudaStream_t)cuda_stream : h->own_stream;
+  return KREA_CUDA_OK;
+}
+
+uint64_t krea_cuda_launch_count(krea_cuda* h) { return h ? h->launches : 0; }
+
+int krea_cuda_sync(krea_cuda* h) {
+  if (!h) return KREA_CUDA_E_ARG;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaMemcpyAsync(h->status_host, h->status_dev, 4, cudaMemcpyDeviceToHost, h->stream));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  const uint32_t st = h->status_host[0];
+  if (st != 0) {
+    cudaMemsetAsync(h->status_dev, 0, 4, h->stream);
+    cudaStreamSynchronize(h->stream);
+    return fail(h, KREA_CUDA_E_DEVICE, "attention kernel gave up on a bounded wait: site %u, query block %u, head %u",
+                st & 0xFFu, (st >> 8) & 0xFFFu, st >> 20);
+  }
+  return KREA_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+int krea_cuda_qk_norm_rope(krea_cuda* h, const krea_cuda_qknorm_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: null handle or arguments");
+  if (a->rows < 0 || a->n_q < 0 || a->n_k < 0) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: negative size");
+  if (a->rows == 0 || a->n_q + a->n_k == 0) return KREA_CUDA_OK;
+  if (!a->qkv || (a->n_q > 0 && !a->wq) || (a->n_k > 0 && !a->wk)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: null tensor");
+  if (a->rope_mode < 0 || a->rope_mode > 2) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: rope_mode must be 0, 1 or 2");
+  if (a->rope_mode != KREA_CUDA_ROPE_NONE && (!a->cos || !a->sin)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: cos/sin tables missing");
+  if (a->ld % 4 || a->q_off % 4 || a->k_off % 4 || ((uintptr_t)a->qkv & 7u))
+    return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: ld, q_off, k_off must be multiples of 4 and qkv 8-byte aligned");
+  if (a->q_off < 0 || a->k_off < 0 || (a->n_q > 0 && a->q_off + a->n_q * 128 > a->ld) || (a->n_k > 0 && a->k_off + a->n_k * 128 > a->ld))
+    return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: heads do not fit in a row of ld elements");
+  if (a->big_dim >= 128) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: big_dim out of range");
+  // the reference throws here too (engine/src/metal.mm:185)
+  if (a->big_dim >= 0 && (!a->qbig || !a->kbig)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: big_dim needs qbig / kbig");
+  NormRopeParams p{};
+  p.src = (const __nv_bfloat16*)a->qkv;
+  p.dst = (__nv_bfloat16*)a->qkv;
+  p.ld_src = p.ld_dst = a->ld;
+  p.bs_src = p.bs_dst = 0;
+  p.rows = a->rows;
+  p.batch = 1;
+  p.q_off = p.q_off_dst = a->q_off;
+  p.k_off = p.k_off_dst = a->k_off;
+  p.n_q = a->n_q;
+  p.n_k = a->n_k;
+  p.wq = a->wq;
+  p.wk = a->wk;
+  p.cos = a->cos;
+  p.sin = a->sin;
+  p.row0 = 0;
+  p.eps = a->eps;
+  p.rope_mode = a->rope_mode;
+  p.big_dim = a->big_dim < 0 ? -1 : a->big_dim;
+  p.qbig = a->qbig;
+  p.kbig = a->kbig;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, launch_qk_norm_rope(p, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+static int make_kv_map(krea_cuda* h, CUtensorMap* tm, const void* base, int cols, int rows, int batch, int64_t ld, int64_t bs,
+                       const char* what) {
+  // (column, row, sample) view; boxes of 64 columns x 128 rows; rows past `rows` read as zero
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? bs : (int64_t)rows * ld) * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = h->encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(h, KREA_CUDA_E_CUDA, "attention: cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
+  return KREA_CUDA_OK;
+}
+
+struct AttnCall {
+  const void *Q, *K, *V, *G;
+  void* O;
+  int batch, Lq, Lk, heads, group;
+  int64_t ldq, ldk, ldv, ldo, ldg, bsq, bsk, bsv, bso, bsg;
+  const float *wq, *cos, *sin;
+  float eps;
+  int rope_mode, q_row0;
+  const int32_t* text_len;
+  int text_slots;
+};
+
+static int run_attention(krea_cuda* h, const AttnCall& c) {
+  if (c.Lq < 0 || c.Lk < 0 || c.heads < 0 || c.batch < 0) return fail(h, KREA_CUDA_E_ARG, "attention: negative size");
+  if (c.Lq == 0 || c.heads == 0 || c.batch == 0) return KREA_CUDA_OK;
+  if (c.group < 1 || c.heads % c.group) return fail(h, KREA_CUDA_E_ARG, "attention: heads must be a multiple of group");
+  if (!c.Q || !c.O || (c.Lk > 0 && (!c.K || !c.V))) return fail(h, KREA_CUDA_E_ARG, "attention: null tensor");
+  const int kvheads = c.heads / c.group;
+  if (c.ldq < (int64_t)c.heads * 128 || c.ldo < (int64_t)c.heads * 128 || c.ldk < (int64_t)kvheads * 128 || c.ldv < (int64_t)kvheads * 128)
+    return fail(h, KREA_CUDA_E_ARG, "attention: a leading dimension is smaller than heads*128");
+  if (c.G && c.ldg < (int64_t)c.heads * 128) return fail(h, KREA_CUDA_E_ARG, "attention: ldg smaller than heads*128");
+  if ((c.ldq | c.ldk | c.ldv | c.ldo | c.ldg | c.bsq | c.bsk | c.bsv | c.bso | c.bsg) % 8)
+    return fail(h, KREA_CUDA_E_ARG, "attention: leading dimensions and batch strides must be multiples of 8 elements");
+  if (!aligned16(c.Q) || !aligned16(c.K) || !aligned16(c.V) || !aligned16(c.O) || !aligned16(c.G))
+    return fail(h, KREA_CUDA_E_ARG, "attention: tensor pointers must be 16-byte aligned");
+  if (c.batch > 65535 || c.heads > 65535) return fail(h, KREA_CUDA_E_ARG, "attention: batch and heads are limited to 65535");
+  if (c.text_len && (c.text_slots <= 0 || c.text_slots > c.Lk)) return fail(h, KREA_CUDA_E_ARG, "attention: text_slots must be in (0, Lk]");
+  if (c.wq && c.rope_mode != KREA_CUDA_ROPE_NONE && (!c.cos || !c.sin)) return fail(h, KREA_CUDA_E_ARG, "attention: cos/sin tables missing");
+  if (c.wq && (((uintptr_t)c.wq | (uintptr_t)c.cos | (uintptr_t)c.sin) & 15u)) return fail(h, KREA_CUDA_E_ARG, "attention: wq/cos/sin must be 16-byte aligned");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+
+  AttnParams p{};
+  p.Q = (const __nv_bfloat16*)c.Q;
+  p.O = (__nv_bfloat16*)c.O;
+  p.G = (const __nv_bfloat16*)c.G;
+  p.ldq = c.ldq; p.ldo = c.ldo; p.ldg = c.ldg;
+  p.bsq = c.bsq; p.bso = c.bso; p.bsg = c.bsg;
+  p.Lq = c.Lq; p.Lk = c.Lk; p.heads = c.heads; p.group = c.group; p.batch = c.batch;
+  p.scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);   // engine/src/metal.mm:198
+  p.wq = c.wq; p.cos = c.cos; p.sin = c.sin; p.eps = c.eps; p.rope_mode = c.rope_mode; p.q_row0 = c.q_row0;
+  p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
+  p.status = h->status_dev;
+
+  CUtensorMap tmK, tmV;
+  memset(&tmK, 0, sizeof(tmK));
+  memset(&tmV, 0, sizeof(tmV));
+  if (c.Lk > 0) {
+    int rc = make_kv_map(h, &tmK, c.K, kvheads * 128, c.Lk, c.batch, c.ldk, c.bsk, "K");
+    if (rc) return rc;
+    rc = make_kv_map(h, &tmV, c.V, kvheads * 128, c.Lk, c.batch, c.ldv, c.bsv, "V");
+    if (rc) return rc;
+  }
+  // one 128-row tile per CTA when two would leave most SMs without work
+  int nq = h->nq;
+  CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "attention: null handle or arguments");
+  if (a->causal) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: causal masking (text-encoder caller) is not built");
+  if (a->QB || a->KB) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: the fp32 rank-1 score term (QB/KB) is not built");
+  AttnCall c{};
+  c.Q = a->Q; c.K = a->K; c.V = a->V; c.O = a->O;
+  c.G = (a->G && a->ldg > 0) ? a->G : nullptr;
+  c.batch = a->batch <= 0 ? 1 : a->batch;
+  c.Lq = a->Lq; c.Lk = a->Lk; c.heads = a->heads; c.group = a->group;
+  c.ldq = a->ldq; c.ldk = a->ldk; c.ldv = a->ldv; c.ldo = a->ldo; c.ldg = c.G ? a->ldg : 0;
+  c.bsq = a->bsq; c.bsk = a->bsk; c.bsv = a->bsv; c.bso = a->bso; c.bsg = c.G ? a->bsg : 0;
+  c.wq = nullptr; c.cos = c.sin = nullptr; c.eps = 0.f; c.rope_mode = KREA_CUDA_ROPE_NONE;
+  c.q_row0 = a->q_row0;
+  c.text_len = a->text_len; c.text_slots = a->text_slots;
+  return run_attention(h, c);
+}
+
+// ---------------------------------------------------------------------------------------------------
+size_t krea_cuda_joint_scratch_bytes(const krea_cuda_joint_args* a) {
+  if (!a || a->group < 1 || a->Lk <= 0 || a->heads <= 0) return 0;
+  const size_t batch = a->batch <= 0 ? 1 : (size_t)a->batch;
+  return batch * (size_t)a->Lk * (size_t)(a->heads / a->group) * 128 * 2;
+}
+
+static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+  const int batch = a->batch <= 0 ? 1 : a->batch;
+  const int kvheads = a->heads / a->group;
+  // K pre-pass: normalised + rotated K, written once to scratch [batch, Lk, kvheads*128]
+  NormRopeParams n{};
+  n.src = (const __nv_bfloat16*)a->K;
+  n.dst = (__nv_bfloat16*)kscr;
+  n.ld_src = a->ldk;
+  n.ld_dst = (int64_t)kvheads * 128;
+  n.bs_src = a->bsk;
+  n.bs_dst = (int64_t)a->Lk * kvheads * 128;
+  n.rows = a->Lk;
+  n.batch = batch;
+  n.q_off = n.q_off_dst = 0;
+  n.n_q = 0;
+  n.k_off = n.k_off_dst = 0;
+  n.n_k = kvheads;
+  n.wq = n.wk = a->wk;
+  n.cos = a->cos;
+  n.sin = a->sin;
+  n.row0 = 0;
+  n.eps = a->eps;
+  n.rope_mode = a->rope_mode;
+  n.big_dim = -1;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, launch_qk_norm_rope(n, h->stream));
+  h->launches++;
+
+  AttnCall c{};
+  c.Q = a->Q; c.K = kscr; c.V = a->V; c.O = a->O;
+  c.G = (a->G && a->ldg > 0) ? a->G : nullptr;
+  c.batch = batch; c.Lq = a->Lq; c.Lk = a->Lk; c.heads = a->heads; c.group = a->group;
+  c.ldq = a->ldq; c.ldk = n.ld_dst; c.ldv = a->ldv; c.ldo = a->ldo; c.ldg = c.G ? a->ldg : 0;
+  c.bsq = a->bsq; c.bsk = n.bs_dst; c.bsv = a->bsv; c.bso = a->bso; c.bsg = c.G ? a->bsg : 0;
+  c.wq = a->wq; c.cos = a->cos; c.sin = a->sin; c.eps = a->eps; c.rope_mode = a->rope_mode; c.q_row0 = a->q_row0;
+  c.text_len = a->text_len; c.text_slots = a->text_slots;
+  return run_attention(h, c);
+}
+
+static int validate_joint(krea_cuda* h, const krea_cuda_joint_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "joint_attention: null handle or arguments");
+  if (a->Lq < 0 || a->Lk < 0 || a->heads < 0 || a->q_row0 < 0) return fail(h, KREA_CUDA_E_ARG, "joint_attention: negative size");
+  if (a->group < 1 || a->heads % a->group) return fail(h, KREA_CUDA_E_ARG, "joint_attention: heads must be a multiple of group");
+  if (!a->wq || !a->wk) return fail(h, KREA_CUDA_E_ARG, "joint_attention: QK-norm weights missing");
+  if (a->rope_mode < 0 || a->rope_mode > 2) return fail(h, KREA_CUDA_E_ARG, "joint_attention: rope_mode must be 0, 1 or 2");
+  if (a->rope_mode != KREA_CUDA_ROPE_NONE && (!a->cos || !a->sin)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: cos/sin tables missing");
+  if (a->Lk > 0 && (!a->K || !a->V)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: null tensor");
+  if (a->ldk % 8 || a->bsk % 8 || !aligned16(a->K)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: K must be 16-byte aligned with ld, batch stride multiples of 8");
+  if (a->ldk < (int64_t)(a->heads / a->group) * 128) return fail(h, KREA_CUDA_E_ARG, "joint_attention: ldk smaller than kv heads*128");
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_args* a) {
+  int rc = validate_joint(h, a);
+  if (rc) return rc;
+  if (a->Lq == 0 || a->heads == 0) return KREA_CUDA_OK;
+  const size_t need = krea_cuda_joint_scratch_bytes(a);
+  void* kscr = a->k_scratch;
+  if (kscr) {
+    if (a->k_scratch_bytes < need) return fail(h, KREA_CUDA_E_NOMEM, "joint_attention: k_scratch holds %zu bytes, %zu needed", a->k_scratch_bytes, need);
+    if (!aligned16(kscr)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: k_scratch must be 16-byte aligned");
+  } else if (need > 0) {
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    if (h->ws_bytes < need) {
+      // growing the workspace: earlier kernels may still be reading the old one
+      CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+      if (h->ws) cudaFree(h->ws);
+      h->ws = nullptr;
+      h->ws_bytes = 0;
+      if (cudaMalloc(&h->ws, need) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, KREA_CUDA_E_NOMEM, "joint_attention: cannot allocate %zu bytes of scratch", need);
+      }
+      h->ws_bytes = need;
+    }
+    kscr = h->ws;
+  }
+  if (a->Lk == 0) {
+    AttnCall c{};
+    c.Q = a->Q; c.O = a->O; c.batch = a->batch <= 0 ? 1 : a->batch; c.Lq = a->Lq; c.Lk = 0; c.heads = a->heads; c.group = a->group;
+    c.ldq = a->ldq; c.ldk = c.ldv = (int64_t)(a->heads / a->group) * 128; c.ldo = a->ldo; c.bsq = a->bsq; c.bso = a->bso;
+    c.K = c.V = a->Q;
+    return run_attention(h, c);
+  }
+  return joint_on_device(h, a, kscr);
+}
+
+static int stage_buf(krea_cuda* h, int slot, size_t bytes, void** out) {
+  if (h->stage_bytes[slot] < bytes) {
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    if (h->stage[slot]) cudaFree(h->stage[slot]);
+    h->stage[slot] = nullptr;
+    h->stage_bytes[slot] = 0;
+    if (cudaMalloc(&h->stage[slot], bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(h, KREA_CUDA_E_NOMEM, "joint_attention_host: cannot allocate %zu bytes", bytes);
+    }
+    h->stage_bytes[slot] = bytes;
+  }
+  *out = h->stage[slot];
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_joint_attention_host(krea_cuda* h, const krea_cuda_joint_args* a) {
+  int rc = validate_joint(h, a);
+  if (rc) return rc;
+  if (!a->Q || !a->O) return fail(h, KREA_CUDA_E_ARG, "joint_attention_host: null tensor");
+  if (a->Lq == 0 || a->heads == 0 || a->Lk == 0) return fail(h, KREA_CUDA_E_ARG, "joint_attention_host: empty problem");
+  if (a->G) return fail(h, KREA_CUDA_E_UNSUPPORTED, "joint_attention_host: the gate is only available through device pointers");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  const int batch = a->batch <= 0 ? 1 : a->batch;
+  const int kvheads = a->heads / a->group;
+  const size_t qw = (size_t)a->heads * 128, kw = (size_t)kvheads * 128;
+  const int trows = a->q_row0 + a->Lq > a->Lk ? a->q_row0 + a->Lq : a->Lk;
+  void *dQ, *dK, *dV, *dO, *dT, *dW, *dL;
+  if ((rc = stage_buf(h, 0, (size_t)batch * a->Lq * qw * 2, &dQ))) return rc;
+  if ((rc = stage_buf(h, 1, (size_t)batch * a->Lk * kw * 2, &dK))) return rc;
+  if ((rc = stage_buf(h, 2, (size_t)batch * a->Lk * kw * 2, &dV))) return rc;
+  if ((rc = stage_buf(h, 3, (size_t)batch * a->Lq * qw * 2, &dO))) return rc;
+  if ((rc = stage_buf(h, 4, (size_t)trows * 64 * 4 * 2, &dT))) return rc;
+  if ((rc = stage_buf(h, 5, 1024, &dW))) return rc;
+  if ((rc = stage_buf(h, 6, (size_t)batch * 4 + 16, &dL))) return rc;
+  for (int b = 0; b < batch; b++) {
+    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dQ + (size_t)b * a->Lq * qw * 2, qw * 2, (const char*)a->Q + (size_t)b * a->bsq * 2, (size_t)a->ldq * 2,
+                                  qw * 2, a->Lq, cudaMemcpyHostToDevice, h->stream));
+    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dK + (size_t)b * a->Lk * kw * 2, kw * 2, (const char*)a->K + (size_t)b * a->bsk * 2, (size_t)a->ldk * 2,
+                                  kw * 2, a->Lk, cudaMemcpyHostToDevice, h->stream));
+    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dV + (size_t)b * a->Lk * kw * 2, kw * 2, (const char*)a->V + (size_t)b * a->bsv * 2, (size_t)a->ldv * 2,
+                                  kw * 2, a->Lk, cudaMemcpyHostToDevice, h->stream));
+  }
+  float* dcos = (float*)dT;
+  float* dsin = dcos + (size_t)trows * 64;
+  if (a->rope_mode != KREA_CUDA_ROPE_NONE) {
+    CUDA_TRY(h, cudaMemcpyAsync(dcos, a->cos, (size_t)trows * 64 * 4, cudaMemcpyHostToDevice, h->stream));
+    CUDA_TRY(h, cudaMemcpyAsync(dsin, a->sin, (size_t)trows * 64 * 4, cudaMemcpyHostToDevice, h->stream));
+  }
+  CUDA_TRY(h, cudaMemcpyAsync(dW, a->wq, 512, cudaMemcpyHostToDevice, h->stream));
+  CUDA_TRY(h, cudaMemcpyAsync((char*)dW + 512, a->wk, 512, cudaMemcpyHostToDevice, h->stream));
+  if (a->text_len) CUDA_TRY(h, cudaMemcpyAsync(dL, a->text_len, (size_t)batch * 4, cudaMemcpyHostToDevice, h->stream));
+  krea_cuda_joint_args d = *a;
+  d.Q = dQ; d.K = dK; d.V = dV; d.O = dO;
+  d.batch = batch;
+  d.ldq = d.ldo = (int)qw; d.ldk = d.ldv = (int)kw;
+  d.bsq = d.bso = (int64_t)a->Lq * qw; d.bsk = d.bsv = (int64_t)a->Lk * kw;
+  d.wq = (const float*)dW; d.wk = (const float*)dW + 128;
+  d.cos = dcos; d.sin = dsin;
+  d.text_len = a->text_len ? (const int32_t*)dL : nullptr;
+  d.G = nullptr; d.ldg = 0; d.bsg = 0;
+  d.k_scratch = nullptr; d.k_scratch_bytes = 0;
+  if ((rc = krea_cuda_joint_attention(h, &d))) return rc;
+  for (int b = 0; b < batch; b++)
+    CUDA_TRY(h, cudaMemcpy2DAsync((char*)a->O + (size_t)b * a->bso * 2, (size_t)a->ldo * 2, (const char*)dO + (size_t)b * a->Lq * qw * 2, qw * 2,
+                                  qw * 2, a->Lq, cudaMemcpyDeviceToHost, h->stream));
+  return krea_cuda_sync(h);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// RoPE tables on the host, like DiT::set_grid (engine/src/model.mm:290-315): frequencies in double,
+// tables stored as f32 [T + gh*gw, 64]; text rows at position 0, image token k at (k / gw, k % gw).
+static void fill_tables(float* c, float* s, int T, int gh, int gw, const double* om, const int* axis) {
+  const int R = T + gh * gw;
+  for (int r = 0; r < R; r++) {
+    const int k = r - T;
+    const double pos[3] = {0.0, r < T ? 0.0 : (double)(k / gw), r < T ? 0.0 : (double)(k % gw)};
+    for (int pr = 0; pr < 64; pr++) {
+      const double ang = pos[axis[pr]] * om[pr];
+      c[(size_t)r * 64 + pr] = (float)cos(ang);
+      s[(size_t)r * 64 + pr] = (float)sin(ang);
+    }
+  }
+}
+
+int krea_cuda_rope_tables_ref3axis(float* c, float* s, int T, int gh, int gw) {
+  if (!c || !s || T < 0 || gh < 0 || gw < 0 || (gh > 0 && gw == 0)) return KREA_CUDA_E_ARG;
+  double om[64];
+  int axis[64];
+  for (int pr = 0; pr < 64; pr++) {
+    axis[pr] = pr < 16 ? 0 : pr < 40 ? 1 : 2;
+    const int first = axis[pr] == 0 ? 0 : axis[pr] == 1 ? 16 : 40;
+    const int dims = axis[pr] == 0 ? 32 : 48;
+    om[pr] = 1.0 / pow(1000.0, (2.0 * (pr - first)) / dims);
+  }
+  fill_tables(c, s, T, gh, gw, om, axis);
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_rope_tables_axial2d(float* c, float* s, int T, int gh, int gw, double theta) {
+  if (!c || !s || T < 0 || gh < 0 || gw < 0 || (gh > 0 && gw == 0) || !(theta > 0)) return KREA_CUDA_E_ARG;
+  double om[64];
+  int axis[64];
+  for (int pr = 0; pr < 64; pr++) {
+    axis[pr] = pr < 32 ? 1 : 2;
+    om[pr] = 1.0 / pow(theta, (2.0 * (pr & 31)) / 64.0);
+  }
+  fill_tables(c, s, T, gh, gw, om, axis);
+  return KREA_CUDA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+static int reshard(krea_cuda* h, const krea_cuda_reshard_args* a, bool unpack) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "reshard: null handle or arguments");
+  if (a->nranks < 1 || a->rows < 0 || a->cols_per_rank < 0) return fail(h, KREA_CUDA_E_ARG, "reshard: bad sizes");
+  if (a->rows == 0 || a->cols_per_rank == 0) return KREA_CUDA_OK;
+  if (!a->src || !a->dst || !aligned16(a->src) || !aligned16(a->dst)) return fail(h, KREA_CUDA_E_ARG, "reshard: null or misaligned pointer");
+  const int ld = unpack ? a->dst_ld : a->src_ld, col0 = unpack ? a->dst_col0 : a->src_col0;
+  if (a->cols_per_rank % 8 || ld % 8 || col0 % 8 || col0 < 0) return fail(h, KREA_CUDA_E_ARG, "reshard: columns and leading dimension must be multiples of 8");
+  if ((int64_t)col0 + (int64_t)a->nranks * a->cols_per_rank > ld) return fail(h, KREA_CUDA_E_ARG, "reshard: column blocks exceed the leading dimension");
+  ReshardParams p{};
+  p.src = (const __nv_bfloat16*)a->src;
+  p.dst = (__nv_bfloat16*)a->dst;
+  p.nranks = a->nranks;
+  p.rows = a->rows;
+  p.cols_per_rank = a->cols_per_rank;
+  p.src_ld = a->src_ld;
+  p.dst_ld = a->dst_ld;
+  p.src_col0 = a->src_col0;
+  p.dst_col0 = a->dst_col0;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, unpack ? launch_reshard_unpack(p, h->stream) : launch_reshard_pack(p, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+int krea_cuda_reshard_pack(krea_cuda* h, const krea_cuda_reshard_args* a) { return reshard(h, a, false); }
+int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a) { return reshard(h, a, true); }
+
+}  // extern "C"

@@ -1,0 +1,149 @@
+"""Host-side mirror of the reference's operator API for the attention path.
+
+`KreaCuda` plays the role of the reference's `class Metal` (engine/src/metal.h:46-165) for its two
+attention-path methods, with the same names, argument order, units (elements) and layouts:
+
+    Metal::qk_norm_rope(qkv, wq, wk, cos, sin, rows, ld, q_off, n_q, k_off, n_k, eps, mode, big_dim, qbig, kbig)
+    Metal::attention(Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, group, causal, q_pos0, G, ldg, QB, KB)
+
+A "Tensor" here is a torch CUDA tensor (or an int device address): only its data pointer crosses the C
+ABI; torch supplies device memory and streams, nothing else.  Like the reference, the operators enqueue
+work and return; `wait()` is the counterpart of Metal::wait.  Errors raise `KreaCudaError` (the
+reference throws std::runtime_error inside and returns -1 + message at its C ABI).
+"""
+import ctypes
+
+from . import binding as B
+
+
+class KreaCudaError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+def _ptr(t):
+    """Device (or host) address of a tensor-like: torch tensor, numpy array, int, or None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    if hasattr(t, "ctypes"):
+        return t.ctypes.data
+    raise TypeError(f"cannot take the address of {type(t)}")
+
+
+class KreaCuda:
+    def __init__(self, device: int = 0):
+        self.lib = B.load()
+        err = ctypes.create_string_buffer(1024)
+        self.h = self.lib.krea_cuda_create(device, err, 1024)
+        if not self.h:
+            raise KreaCudaError(B.E_CUDA, err.value.decode() or "krea_cuda_create failed")
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.krea_cuda_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != B.OK:
+            raise KreaCudaError(rc, self.lib.krea_cuda_last_error(self.h).decode())
+
+    # ---- stream handling --------------------------------------------------------------------------
+    def set_stream(self, stream):
+        """stream: a torch.cuda.Stream, a raw cudaStream_t address, or None for the handle's own."""
+        s = None if stream is None else getattr(stream, "cuda_stream", stream)
+        self._check(self.lib.krea_cuda_set_stream(self.h, s))
+
+    def wait(self):
+        """Block until the stream is idle; raises if a kernel reported a timed-out wait."""
+        self._check(self.lib.krea_cuda_sync(self.h))
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.krea_cuda_launch_count(self.h))
+
+    # ---- Metal::qk_norm_rope (engine/src/metal.h:80-82) ---------------------------------------------
+    def qk_norm_rope(self, qkv, wq, wk, cos, sin, rows, ld, q_off, n_q, k_off, n_k, eps, mode=B.ROPE_PAIRS, big_dim=-1,
+                     qbig=None, kbig=None):
+        a = B.QKNormArgs(_ptr(qkv), _ptr(wq), _ptr(wk), _ptr(cos), _ptr(sin), rows, ld, q_off, n_q, k_off, n_k, eps,
+                         int(mode), big_dim, _ptr(qbig), _ptr(kbig))
+        self._check(self.lib.krea_cuda_qk_norm_rope(self.h, ctypes.byref(a)))
+
+    # ---- Metal::attention (engine/src/metal.h:83-88) ------------------------------------------------
+    def attention(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, group=1, causal=False, q_pos0=0, G=None, ldg=0,
+                  QB=None, KB=None, *, batch=1, bsq=0, bsk=0, bsv=0, bso=0, bsg=0, text_len=None, text_slots=0, q_row0=0):
+        a = B.AttnArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), Lq, Lk, heads, ldq, ldk, ldv, ldo, group, int(bool(causal)),
+                       q_pos0, _ptr(G), ldg, _ptr(QB), _ptr(KB), batch, bsq, bsk, bsv, bso, bsg, _ptr(text_len),
+                       text_slots, q_row0)
+        self._check(self.lib.krea_cuda_attention(self.h, ctypes.byref(a)))
+
+    # ---- DiT::qk_rope + DiT::attend in one call (engine/src/model.mm:271-288) -----------------------
+    def _joint_args(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps, group, rope_mode, q_row0,
+                    batch, bsq, bsk, bsv, bso, text_len, text_slots, G, ldg, bsg, k_scratch, k_scratch_bytes):
+        return B.JointArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), batch, Lq, Lk, q_row0, heads, group, ldq, ldk, ldv, ldo,
+                           bsq, bsk, bsv, bso, _ptr(wq), _ptr(wk), _ptr(cos), _ptr(sin), eps, int(rope_mode),
+                           _ptr(text_len), text_slots, _ptr(G), ldg, bsg, _ptr(k_scratch), k_scratch_bytes)
+
+    def joint_attention(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps=1e-6, group=1,
+                        rope_mode=B.ROPE_PAIRS, q_row0=0, *, batch=1, bsq=0, bsk=0, bsv=0, bso=0, text_len=None,
+                        text_slots=0, G=None, ldg=0, bsg=0, k_scratch=None, k_scratch_bytes=0):
+        a = self._joint_args(Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps, group, rope_mode,
+                             q_row0, batch, bsq, bsk, bsv, bso, text_len, text_slots, G, ldg, bsg, k_scratch,
+                             k_scratch_bytes)
+        self._check(self.lib.krea_cuda_joint_attention(self.h, ctypes.byref(a)))
+
+    def joint_attention_host(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps=1e-6, group=1,
+                             rope_mode=B.ROPE_PAIRS, q_row0=0, *, batch=1, bsq=0, bsk=0, bsv=0, bso=0, text_len=None,
+                             text_slots=0):
+        """Every argument lives in host memory (numpy arrays or pinned torch tensors); returns after O is back."""
+        a = self._joint_args(Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps, group, rope_mode,
+                             q_row0, batch, bsq, bsk, bsv, bso, text_len, text_slots, None, 0, 0, None, 0)
+        self._check(self.lib.krea_cuda_joint_attention_host(self.h, ctypes.byref(a)))
+
+    def joint_scratch_bytes(self, Lk, heads, group=1, batch=1) -> int:
+        a = B.JointArgs()
+        a.Lk, a.heads, a.group, a.batch = Lk, heads, group, batch
+        return int(self.lib.krea_cuda_joint_scratch_bytes(ctypes.byref(a)))
+
+    # ---- sequence <-> head resharding ---------------------------------------------------------------
+    def reshard_pack(self, src, dst, nranks, rows, cols_per_rank, src_ld, src_col0=0):
+        a = B.ReshardArgs(_ptr(src), _ptr(dst), nranks, rows, cols_per_rank, src_ld, 0, src_col0, 0)
+        self._check(self.lib.krea_cuda_reshard_pack(self.h, ctypes.byref(a)))
+
+    def reshard_unpack(self, src, dst, nranks, rows, cols_per_rank, dst_ld, dst_col0=0):
+        a = B.ReshardArgs(_ptr(src), _ptr(dst), nranks, rows, cols_per_rank, 0, dst_ld, 0, dst_col0)
+        self._check(self.lib.krea_cuda_reshard_unpack(self.h, ctypes.byref(a)))
+
+
+def rope_tables_ref3axis(T, gh, gw):
+    """DiT::set_grid (engine/src/model.mm:290-315): numpy f32 cos/sin [T + gh*gw, 64] built by the library."""
+    import numpy as np
+    lib = B.load()
+    c = np.empty((T + gh * gw, 64), dtype=np.float32)
+    s = np.empty_like(c)
+    rc = lib.krea_cuda_rope_tables_ref3axis(c.ctypes.data, s.ctypes.data, T, gh, gw)
+    if rc:
+        raise KreaCudaError(rc, "rope_tables_ref3axis: bad arguments")
+    return c, s
+
+
+def rope_tables_axial2d(T, gh, gw, theta=10000.0):
+    import numpy as np
+    lib = B.load()
+    c = np.empty((T + gh * gw, 64), dtype=np.float32)
+    s = np.empty_like(c)
+    rc = lib.krea_cuda_rope_tables_axial2d(c.ctypes.data, s.ctypes.data, T, gh, gw, theta)
+    if rc:
+        raise KreaCudaError(rc, "rope_tables_axial2d: bad arguments")
+    return c, s

@@ -1,0 +1,80 @@
+"""Independent float64 numpy statement of the same formulas as krea_oracle.c (small shapes only).
+
+Test infrastructure.  Written from the formulas, not from the C file, so that a slip in either shows up
+as a disagreement: RMSNorm (norm.metal:102-103), interleaved-pair RoPE (norm.metal:105-113),
+softmax(q.k/sqrt(128)) with masked keys removed (attention.metal:237-249,270-271), P V / l with an empty
+row giving zeros (attention.metal:316), sigmoid gate (attention.metal:321-329).
+"""
+import numpy as np
+
+
+def bf16_bits_to_f64(u16: np.ndarray) -> np.ndarray:
+    return (u16.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even to bf16, returned as float64."""
+    f = np.asarray(x, dtype=np.float32)
+    u = f.view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).astype(np.float64)
+
+
+def norm_rope(x, w, cos, sin, eps, rope_mode=0):
+    """x [..., S, 128] float64; cos/sin [S, 64]."""
+    rrms = 1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
+    y = x * rrms * w
+    if rope_mode == 2:
+        return y
+    out = np.empty_like(y)
+    if rope_mode == 0:
+        a, b = y[..., 0::2], y[..., 1::2]
+        out[..., 0::2] = a * cos - b * sin
+        out[..., 1::2] = a * sin + b * cos
+    else:
+        a, b = y[..., :64], y[..., 64:]
+        out[..., :64] = a * cos - b * sin
+        out[..., 64:] = b * cos + a * sin
+    return out
+
+
+def attention_core(q, k, v, key_ok=None, causal=False, q_pos0=0, round_p=False):
+    """q [Lq,128], k/v [Lk,128] float64.  key_ok bool [Lk]."""
+    s = (q @ k.T) / np.sqrt(128.0)
+    ok = np.ones(s.shape, dtype=bool)
+    if key_ok is not None:
+        ok &= key_ok[None, :]
+    if causal:
+        ok &= np.arange(k.shape[0])[None, :] <= (np.arange(q.shape[0])[:, None] + q_pos0)
+    s = np.where(ok, s, -np.inf)
+    m = s.max(axis=1, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    p = np.exp(s - m)
+    l = p.sum(axis=1, keepdims=True)
+    pv = round_bf16(p) if round_p else p
+    o = pv @ v
+    return np.where(l > 0, o / np.where(l > 0, l, 1.0), 0.0)
+
+
+def joint_attention(qkv_bits, B, S, heads, wq, wk, cos, sin, eps=1e-6, rope_mode=0, text_len=None, text_slots=0,
+                    ref_rounding=False):
+    """qkv_bits uint16 [B, S, 3*heads*128] (group = 1).  Returns float64 [B, S, heads*128]."""
+    x = bf16_bits_to_f64(qkv_bits).reshape(B, S, 3, heads, 128)
+    cos = cos.astype(np.float64)
+    sin = sin.astype(np.float64)
+    out = np.zeros((B, S, heads, 128))
+    for b in range(B):
+        key_ok = None
+        if text_len is not None:
+            idx = np.arange(S)
+            key_ok = ~((idx >= text_len[b]) & (idx < text_slots))
+        for h in range(heads):
+            q = norm_rope(x[b, :, 0, h], wq.astype(np.float64), cos, sin, eps, rope_mode)
+            k = norm_rope(x[b, :, 1, h], wk.astype(np.float64), cos, sin, eps, rope_mode)
+            if ref_rounding:
+                q, k = round_bf16(q), round_bf16(k)
+            o = attention_core(q, k, x[b, :, 2, h], key_ok, round_p=ref_rounding)
+            if key_ok is not None:
+                o[~key_ok] = 0.0
+            out[b, :, h] = round_bf16(o) if ref_rounding else o
+    return out.reshape(B, S, heads * 128)

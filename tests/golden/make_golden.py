@@ -1,0 +1,72 @@
+"""Regenerate tests/golden/*.npz from the CPU oracle.
+
+    python tests/golden/make_golden.py
+
+The reference ships no golden vectors for the attention path (and cannot run off macOS), so these
+fixtures do not pin the oracle to the reference; they pin the oracle - and the seeded input generator -
+against drift, and give the GPU parity tests committed expected values that travel with the repository.
+Each file holds the sampled fp32 outputs of the oracle in both rounding modes for one seeded case plus
+checksums of its inputs.
+"""
+import os
+import sys
+import zlib
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+import oracle  # noqa: E402
+from krea_image_b200 import synth  # noqa: E402
+
+
+def crc(a: np.ndarray) -> int:
+    return zlib.crc32(np.ascontiguousarray(a).tobytes())
+
+
+def case_config(cid: int, heads_sel, rows_per_head: int):
+    cfg = synth.CONFIGS[cid]
+    qkv = synth.qkv_slice(cfg)
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    tl = synth.text_lengths(cfg) if cfg.masked else None
+    rng = np.random.default_rng(1000 + cid)
+    out = {"cid": cid, "qkv_crc": crc(qkv), "wq_crc": crc(wq), "wk_crc": crc(wk), "cos_crc": crc(cos), "sin_crc": crc(sin),
+           "heads": np.array(heads_sel, dtype=np.int32)}
+    if tl is not None:
+        out["text_len"] = tl
+    rows_all, f32_all, ref_all, b_all = [], [], [], []
+    for b in range(cfg.batch if cfg.masked else 1):
+        for h in heads_sel:
+            rows = np.sort(rng.choice(cfg.seq, size=rows_per_head, replace=False)).astype(np.int32)
+            rows[0], rows[-1] = 0, cfg.seq - 1
+            kw = dict(text_len=int(tl[b]) if tl is not None else -1, text_slots=cfg.text if tl is not None else 0)
+            f32_all.append(oracle.joint_attention_rows(qkv[b], cfg.seq, cfg.heads, h, wq, wk, cos, sin, rows, **kw))
+            ref_all.append(oracle.joint_attention_rows(qkv[b], cfg.seq, cfg.heads, h, wq, wk, cos, sin, rows,
+                                                       ref_rounding=True, **kw))
+            rows_all.append(rows)
+            b_all.append(b)
+    out["rows"] = np.stack(rows_all)
+    out["sample"] = np.array(b_all, dtype=np.int32)
+    out["head_of_block"] = np.array([h for _ in range(cfg.batch if cfg.masked else 1) for h in heads_sel], dtype=np.int32)
+    out["fp32"] = np.stack(f32_all)
+    out["ref"] = np.stack(ref_all)
+    return out
+
+
+def main():
+    np.savez_compressed(os.path.join(HERE, "c0_rows.npz"), **case_config(0, [0, 7, 23], 24))
+    np.savez_compressed(os.path.join(HERE, "c1_rows.npz"), **case_config(1, [0, 11, 23], 16))
+    np.savez_compressed(os.path.join(HERE, "c2_rows.npz"), **case_config(2, [3, 20], 12))
+    # generator known answers: first values of a few streams
+    ka = {f"normal_seed{sd}_first{fi}": oracle.gen_normal_bf16(sd, fi, 16) for sd, fi in ((1234, 0), (1235, 7), (1238, 1 << 33))}
+    ka["uniform_1234"] = oracle.gen_uniform_f32(1234, 3 << 40, 0.5, 1.5, 8)
+    np.savez_compressed(os.path.join(HERE, "generator_kat.npz"), **ka)
+    for f in sorted(os.listdir(HERE)):
+        if f.endswith(".npz"):
+            print(f, os.path.getsize(os.path.join(HERE, f)))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+"""CPU tests of the drop-in boundary: the shared library builds, loads without a GPU, exports exactly
+what include/krea_cuda.h declares, and its host-side pieces (RoPE table builders, argument checks that
+need no device) behave like the reference's (engine/src/model.mm:290-315, engine/src/metal.mm:182-202)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+
+import oracle
+from krea_image_b200 import binding, ops
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "krea_cuda.h")).read()
+    return re.findall(r"KREA_CUDA_API\s+[\w\s\*]+?\b(krea_cuda_\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = binding.load()
+    names = _declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(binding.SYMBOLS), set(names) ^ set(binding.SYMBOLS)
+
+
+def test_library_is_built_in_tree():
+    assert binding.library_path().startswith(ROOT)
+    assert os.path.exists(binding.library_path())
+
+
+def test_struct_layouts_match_header_field_order():
+    text = open(os.path.join(ROOT, "include", "krea_cuda.h")).read()
+    for cname, st in (("krea_cuda_qknorm_args", binding.QKNormArgs), ("krea_cuda_attn_args", binding.AttnArgs),
+                      ("krea_cuda_joint_args", binding.JointArgs), ("krea_cuda_reshard_args", binding.ReshardArgs)):
+        end = text.index("} " + cname + ";")
+        body = text[text.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        fields = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            names = [re.sub(r"[\*\s]", "", n.split()[-1]) for n in decl.split(",")]
+            fields += names
+        assert fields == [f[0] for f in st._fields_], cname
+
+
+def test_rope_tables_match_oracle():
+    for T, gh, gw in ((512, 32, 32), (7, 3, 5), (0, 2, 2), (4, 0, 0)):
+        c, s = ops.rope_tables_axial2d(T, gh, gw)
+        c2, s2 = oracle.rope_tables_axial2d(T, gh, gw)
+        assert np.allclose(c, c2, atol=1e-7) and np.allclose(s, s2, atol=1e-7)
+        c, s = ops.rope_tables_ref3axis(T, gh, gw)
+        c2, s2 = oracle.rope_tables_ref3axis(T, gh, gw)
+        assert np.allclose(c, c2, atol=1e-7) and np.allclose(s, s2, atol=1e-7)
+
+
+def test_host_side_argument_errors():
+    lib = binding.load()
+    assert lib.krea_cuda_rope_tables_axial2d(None, None, 1, 1, 1, 10000.0) == binding.E_ARG
+    assert lib.krea_cuda_rope_tables_ref3axis(None, None, 1, 1, 1) == binding.E_ARG
+    # null handles are rejected, never dereferenced
+    assert lib.krea_cuda_sync(None) == binding.E_ARG
+    assert lib.krea_cuda_attention(None, None) == binding.E_ARG
+    assert lib.krea_cuda_qk_norm_rope(None, None) == binding.E_ARG
+    assert lib.krea_cuda_joint_attention(None, None) == binding.E_ARG
+    a = binding.JointArgs()
+    a.Lk, a.heads, a.group, a.batch = 4608, 24, 1, 1
+    assert lib.krea_cuda_joint_scratch_bytes(ctypes.byref(a)) == 4608 * 24 * 128 * 2
+
+
+def test_create_fails_loudly_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        return
+    try:
+        ops.KreaCuda(0)
+    except ops.KreaCudaError as e:
+        assert "CUDA" in str(e) or "device" in str(e)
+    else:
+        raise AssertionError("krea_cuda_create must fail when there is no GPU (no CPU fallback)")

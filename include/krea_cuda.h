@@ -62,6 +62,13 @@ KREA_CUDA_API int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream);
 KREA_CUDA_API int krea_cuda_sync(krea_cuda* h);
 /* Number of kernels this handle has launched so far. */
 KREA_CUDA_API uint64_t krea_cuda_launch_count(krea_cuda* h);
+/* Per-operator GPU timing, the counterpart of the reference's KREA_PROFILE marks (Metal::mark,
+ * engine/src/metal.h:126-145): while enabled, every kernel launch is bracketed by CUDA events on the
+ * stream.  krea_cuda_profile_read synchronises the stream and returns the accumulated device time and
+ * launch count of the prologue kernel (which = 0) or the attention kernel (which = 1) since the last
+ * krea_cuda_profile_enable(h, 1), then clears them. */
+KREA_CUDA_API int krea_cuda_profile_enable(krea_cuda* h, int on);
+KREA_CUDA_API int krea_cuda_profile_read(krea_cuda* h, int which, double* total_ms, int* launches);
 
 /* ---- Metal::qk_norm_rope (engine/src/metal.h:80-82; kernel engine/kernels/norm.metal:81-134) ----
  * In place on bf16 rows [rows, ld]: for every row and head, x <- bf16(rope(x * rsqrt(mean(x^2) + eps) * w)).

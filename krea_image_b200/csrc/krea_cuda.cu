@@ -11,6 +11,8 @@
 #include <string.h>
 
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "../../include/krea_cuda.h"
 #include "attention_sm100.h"
@@ -35,6 +37,37 @@ struct krea_cuda {
   uint64_t launches = 0;
   PFN_encodeTiled encode = nullptr;
   int nq = 2;                       // query tiles per CTA
+  bool profiling = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
+  std::vector<cudaEvent_t> event_pool;
+};
+
+// Brackets one kernel launch with events while profiling is on (kind 0 = prologue, 1 = attention).
+struct ProfileMark {
+  krea_cuda* h;
+  int kind;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  static cudaEvent_t get(krea_cuda* h) {
+    if (!h->event_pool.empty()) {
+      cudaEvent_t e = h->event_pool.back();
+      h->event_pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+  ProfileMark(krea_cuda* h_, int kind_) : h(h_), kind(kind_) {
+    if (!h->profiling) return;
+    e0 = get(h);
+    e1 = get(h);
+    if (e0) cudaEventRecord(e0, h->stream);
+  }
+  ~ProfileMark() {
+    if (!e0 || !e1) return;
+    cudaEventRecord(e1, h->stream);
+    h->marks[kind].push_back({e0, e1});
+  }
 };
 
 static int fail(krea_cuda* h, int code, const char* fmt, ...) {
@@ -114,6 +147,12 @@ void krea_cuda_destroy(krea_cuda* h) {
   if (h->ws) cudaFree(h->ws);
   for (int i = 0; i < 8; i++)
     if (h->stage[i]) cudaFree(h->stage[i]);
+  for (int k = 0; k < 2; k++)
+    for (auto& m : h->marks[k]) {
+      cudaEventDestroy(m.first);
+      cudaEventDestroy(m.second);
+    }
+  for (cudaEvent_t e : h->event_pool) cudaEventDestroy(e);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
   delete h;
 }
@@ -127,6 +166,39 @@ int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream) {
 }
 
 uint64_t krea_cuda_launch_count(krea_cuda* h) { return h ? h->launches : 0; }
+
+int krea_cuda_profile_enable(krea_cuda* h, int on) {
+  if (!h) return KREA_CUDA_E_ARG;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  for (int k = 0; k < 2; k++) {
+    for (auto& m : h->marks[k]) {
+      h->event_pool.push_back(m.first);
+      h->event_pool.push_back(m.second);
+    }
+    h->marks[k].clear();
+  }
+  h->profiling = on != 0;
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_profile_read(krea_cuda* h, int which, double* total_ms, int* launches) {
+  if (!h || which < 0 || which > 1 || !total_ms || !launches) return fail(h, KREA_CUDA_E_ARG, "profile_read: bad arguments");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  double sum = 0.0;
+  for (auto& m : h->marks[which]) {
+    float ms = 0.f;
+    CUDA_TRY(h, cudaEventElapsedTime(&ms, m.first, m.second));
+    sum += ms;
+    h->event_pool.push_back(m.first);
+    h->event_pool.push_back(m.second);
+  }
+  *total_ms = sum;
+  *launches = (int)h->marks[which].size();
+  h->marks[which].clear();
+  return KREA_CUDA_OK;
+}
 
 int krea_cuda_sync(krea_cuda* h) {
   if (!h) return KREA_CUDA_E_ARG;
@@ -180,7 +252,10 @@ int krea_cuda_qk_norm_rope(krea_cuda* h, const krea_cuda_qknorm_args* a) {
   p.qbig = a->qbig;
   p.kbig = a->kbig;
   CUDA_TRY(h, cudaSetDevice(h->device));
-  CUDA_TRY(h, launch_qk_norm_rope(p, h->stream));
+  {
+    ProfileMark pm(h, 0);
+    CUDA_TRY(h, launch_qk_norm_rope(p, h->stream));
+  }
   h->launches++;
   return KREA_CUDA_OK;
 }
@@ -254,7 +329,10 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   }
   // one 128-row tile per CTA when two would leave most SMs without work
   int nq = h->nq;
-  CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->stream));
+  {
+    ProfileMark pm(h, 1);
+    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->stream));
+  }
   h->launches++;
   return KREA_CUDA_OK;
 }
@@ -308,7 +386,10 @@ static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* ks
   n.rope_mode = a->rope_mode;
   n.big_dim = -1;
   CUDA_TRY(h, cudaSetDevice(h->device));
-  CUDA_TRY(h, launch_qk_norm_rope(n, h->stream));
+  {
+    ProfileMark pm(h, 0);
+    CUDA_TRY(h, launch_qk_norm_rope(n, h->stream));
+  }
   h->launches++;
 
   AttnCall c{};

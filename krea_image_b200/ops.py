@@ -73,6 +73,16 @@ class KreaCuda:
     def launches(self) -> int:
         return int(self.lib.krea_cuda_launch_count(self.h))
 
+    def profile(self, on: bool):
+        """Per-kernel GPU timing like the reference's KREA_PROFILE marks (engine/src/metal.h:126-145)."""
+        self._check(self.lib.krea_cuda_profile_enable(self.h, int(on)))
+
+    def profile_read(self, which: int):
+        """(total device ms, launches) of the prologue (0) or attention (1) kernel since profile(True)."""
+        ms, n = ctypes.c_double(0), ctypes.c_int(0)
+        self._check(self.lib.krea_cuda_profile_read(self.h, which, ctypes.byref(ms), ctypes.byref(n)))
+        return ms.value, n.value
+
     # ---- Metal::qk_norm_rope (engine/src/metal.h:80-82) ---------------------------------------------
     def qk_norm_rope(self, qkv, wq, wk, cos, sin, rows, ld, q_off, n_q, k_off, n_k, eps, mode=B.ROPE_PAIRS, big_dim=-1,
                      qbig=None, kbig=None):

@@ -1,0 +1,335 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on identical seeded
+inputs.  Tolerances are the ones the north star states for the output: relative-L2 <= 5e-3 and max-abs
+<= 2e-2 against the oracle's fp32 mode; the oracle's reference-rounding mode (which rounds where the
+reference kernels round) must be matched more tightly."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from krea_image_b200 import binding, ops, synth
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+REL_L2_TOL = 5e-3     # vs fp32 oracle
+MAX_ABS_TOL = 2e-2    # vs fp32 oracle
+REL_L2_REF = 2.5e-3   # vs the oracle run with the reference's roundings
+
+
+@pytest.fixture(scope="module")
+def kc():
+    k = ops.KreaCuda(0)
+    k.set_stream(torch.cuda.current_stream())
+    yield k
+    k.close()
+
+
+def dev_bits(a):
+    """uint16 bf16 bits (numpy) -> bf16 CUDA tensor."""
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def host_f32(t):
+    return t.float().cpu().numpy()
+
+
+def dev_f32(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def check(got, want_f32, want_ref=None, what=""):
+    d = got.astype(np.float64) - want_f32
+    rel = np.linalg.norm(d) / max(np.linalg.norm(want_f32), 1e-30)
+    mx = np.abs(d).max()
+    assert np.all(np.isfinite(got)), what
+    assert rel <= REL_L2_TOL and mx <= MAX_ABS_TOL, f"{what}: rel-L2 {rel:.3e} max-abs {mx:.3e} vs fp32 oracle"
+    if want_ref is not None:
+        d = got.astype(np.float64) - want_ref
+        rel_r = np.linalg.norm(d) / max(np.linalg.norm(want_ref), 1e-30)
+        assert rel_r <= REL_L2_REF, f"{what}: rel-L2 {rel_r:.3e} vs reference-rounding oracle"
+    return rel, mx
+
+
+def rand_case(seed, B, S, H, T, gh, gw, group=1):
+    rng = np.random.default_rng(seed)
+    kvh = H // group
+    qkv = synth.f32_to_bf16_bits(rng.standard_normal((B, S, (H + 2 * kvh) * 128)).astype(np.float32))
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    cos, sin = synth.rope_tables_axial2d(T, gh, gw)
+    return qkv, wq, wk, cos, sin
+
+
+def run_joint(kc, qkv, B, S, H, wq, wk, cos, sin, group=1, text_len=None, text_slots=0, rope_mode=0, eps=1e-6):
+    kvh = H // group
+    ld = (H + 2 * kvh) * 128
+    x = dev_bits(qkv)
+    o = torch.full((B, S, H * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    q, k, v = x.view(-1)[0:], x.view(-1)[H * 128:], x.view(-1)[(H + kvh) * 128:]
+    tl = None if text_len is None else torch.from_numpy(np.asarray(text_len, dtype=np.int32)).cuda()
+    kc.joint_attention(q, k, v, o, S, S, H, ld, ld, ld, H * 128, dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin),
+                       eps, group, rope_mode, 0, batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128,
+                       text_len=tl, text_slots=text_slots)
+    kc.wait()
+    return host_f32(o)
+
+
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_qk_norm_rope_operator(kc, mode):
+    """Metal::qk_norm_rope: in place, q and k heads, all three RoPE modes, bf16 store."""
+    rng = np.random.default_rng(20 + mode)
+    rows, n_q, n_k = 300, 5, 3
+    ld = (n_q + n_k) * 128 + 256
+    base = synth.f32_to_bf16_bits(rng.standard_normal((rows, ld)).astype(np.float32))
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    cos, sin = synth.rope_tables_axial2d(44, 16, 16)
+    want = base.copy()
+    oracle.qk_norm_rope(want, wq, wk, cos, sin, rows, ld, 128, n_q, 128 + n_q * 128, n_k, 1e-5, mode)
+    x = dev_bits(base)
+    kc.qk_norm_rope(x, dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin), rows, ld, 128, n_q, 128 + n_q * 128, n_k, 1e-5, mode)
+    kc.wait()
+    got = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    g, w = synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)
+    # identical up to one bf16 ulp where fp32 evaluation order differs (rsqrt approximation, fma)
+    assert np.abs(g - w).max() <= 2.0 ** -7 * max(1.0, np.abs(w).max())
+    assert (got != want).mean() < 0.02
+    assert np.array_equal(got[:, :128], base[:, :128]) and np.array_equal(got[:, 128 + (n_q + n_k) * 128:], base[:, 128 + (n_q + n_k) * 128:])
+
+
+def test_qk_norm_rope_q_only_k_only_and_big_dim(kc):
+    rng = np.random.default_rng(31)
+    rows, n_q, n_k = 130, 4, 2
+    ld = (n_q + n_k) * 128
+    base = synth.f32_to_bf16_bits(rng.standard_normal((rows, ld)).astype(np.float32))
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    cos, sin = synth.rope_tables_ref3axis(30, 10, 10)
+    want = base.copy()
+    qb_w, kb_w = oracle.qk_norm_rope(want, wq, wk, cos, sin, rows, ld, 0, n_q, n_q * 128, n_k, 1e-5, 0, big_dim=77)
+    x = dev_bits(base)
+    qb = torch.zeros(rows, n_q, device="cuda")
+    kb = torch.zeros(rows, n_k, device="cuda")
+    dw = (dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin))
+    # the reference issues the q half and the k half as separate launches in its hybrid schedule (model.mm:427-441)
+    kc.qk_norm_rope(x, *dw, rows, ld, 0, n_q, n_q * 128, 0, 1e-5, 0, 77, qb, kb)
+    kc.qk_norm_rope(x, *dw, rows, ld, 0, 0, n_q * 128, n_k, 1e-5, 0, 77, qb, kb)
+    kc.wait()
+    got = x.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert (got != want).mean() < 0.02
+    assert np.all(got[:, 77::128] == 0)
+    assert np.allclose(qb.cpu().numpy(), qb_w, rtol=1e-3, atol=1e-4) and np.allclose(kb.cpu().numpy(), kb_w, rtol=1e-3, atol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("Lq,Lk,H,group", [(128, 128, 1, 1), (256, 384, 2, 1), (100, 77, 3, 1), (333, 1000, 4, 2), (1152, 1500, 8, 4), (1, 1, 1, 1)])
+def test_attention_operator_shapes(kc, Lq, Lk, H, group):
+    """Metal::attention on already-normalised operands: ragged tails, Lq != Lk, GQA."""
+    rng = np.random.default_rng(Lq * 7 + Lk)
+    kvh = H // group
+    ldq, ldk, ldv, ldo = H * 128 + 64, kvh * 128 + 8, kvh * 128, H * 128 + 128
+    Q = synth.f32_to_bf16_bits(rng.standard_normal((Lq, ldq)).astype(np.float32))
+    K = synth.f32_to_bf16_bits(rng.standard_normal((Lk, ldk)).astype(np.float32))
+    V = synth.f32_to_bf16_bits(rng.standard_normal((Lk, ldv)).astype(np.float32))
+    want = oracle.attention(Q, K, V, Lq, Lk, H, ldq, ldk, ldv, group=group)
+    want_r = oracle.attention(Q, K, V, Lq, Lk, H, ldq, ldk, ldv, group=group, ref_rounding=True)
+    o = torch.full((Lq, ldo), 7.0, dtype=torch.bfloat16, device="cuda")
+    kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, ldq, ldk, ldv, ldo, group, False, 0)
+    kc.wait()
+    got = host_f32(o)
+    check(got[:, :H * 128], want, want_r, f"attention {Lq}x{Lk} H{H} g{group}")
+    assert np.all(got[:, H * 128:] == 7.0)     # columns past heads*128 are not touched
+
+
+def test_attention_gate(kc):
+    rng = np.random.default_rng(41)
+    Lq, Lk, H = 200, 300, 3
+    ld = H * 128
+    Q, K, V, G = (synth.f32_to_bf16_bits(rng.standard_normal((n, ld)).astype(np.float32)) for n in (Lq, Lk, Lk, Lq))
+    want = oracle.attention(Q, K, V, Lq, Lk, H, ld, ld, ld, G=G, ldg=ld)
+    o = torch.zeros((Lq, ld), dtype=torch.bfloat16, device="cuda")
+    kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, ld, ld, ld, ld, 1, False, 0, dev_bits(G), ld)
+    kc.wait()
+    check(host_f32(o), want, None, "gated attention")
+
+
+def test_attention_large_logits_lazy_max(kc):
+    """Scores that keep growing along the key axis force repeated running-max updates and O rescales."""
+    rng = np.random.default_rng(43)
+    Lq, Lk, H = 256, 1024, 1
+    Q = rng.standard_normal((Lq, 128)).astype(np.float32)
+    K = rng.standard_normal((Lk, 128)).astype(np.float32) * np.linspace(0.2, 6.0, Lk, dtype=np.float32)[:, None]
+    V = rng.standard_normal((Lk, 128)).astype(np.float32)
+    Qb, Kb, Vb = (synth.f32_to_bf16_bits(t) for t in (Q, K, V))
+    want = oracle.attention(Qb, Kb, Vb, Lq, Lk, H, 128, 128, 128)
+    want_r = oracle.attention(Qb, Kb, Vb, Lq, Lk, H, 128, 128, 128, ref_rounding=True)
+    o = torch.zeros((Lq, 128), dtype=torch.bfloat16, device="cuda")
+    kc.attention(dev_bits(Qb), dev_bits(Kb), dev_bits(Vb), o, Lq, Lk, H, 128, 128, 128, 128)
+    kc.wait()
+    d = host_f32(o) - want_r
+    assert np.linalg.norm(d) / np.linalg.norm(want_r) < 1e-2 and np.abs(host_f32(o) - want).max() < 5e-2
+
+
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_joint_small_all_rope_modes(kc, mode):
+    qkv, wq, wk, cos, sin = rand_case(50 + mode, 1, 200, 2, 72, 8, 16)
+    want = oracle.joint_attention(qkv, 1, 200, 2, wq, wk, cos, sin, rope_mode=mode, eps=1e-5)
+    want_r = oracle.joint_attention(qkv, 1, 200, 2, wq, wk, cos, sin, rope_mode=mode, eps=1e-5, ref_rounding=True)
+    got = run_joint(kc, qkv, 1, 200, 2, wq, wk, cos, sin, rope_mode=mode, eps=1e-5)
+    check(got, want, want_r, f"joint rope_mode {mode}")
+
+
+def test_joint_gqa_batch_padding_mask(kc):
+    """Batch of 3 with text key-padding, GQA group 2: padded keys ignored, padded query rows zero."""
+    B, H, group, T, gh, gw = 3, 4, 2, 256, 16, 20
+    S = T + gh * gw
+    qkv, wq, wk, cos, sin = rand_case(60, B, S, H, T, gh, gw, group)
+    tl = np.array([256, 77, 130], dtype=np.int32)     # no padding / ends inside tile 0 / ends inside tile 1
+    want = oracle.joint_attention(qkv, B, S, H, wq, wk, cos, sin, text_len=tl, text_slots=T, group=group)
+    want_r = oracle.joint_attention(qkv, B, S, H, wq, wk, cos, sin, text_len=tl, text_slots=T, group=group, ref_rounding=True)
+    got = run_joint(kc, qkv, B, S, H, wq, wk, cos, sin, group=group, text_len=tl, text_slots=T)
+    check(got, want, want_r, "joint masked batch")
+    for b in range(B):
+        assert np.all(got[b, tl[b]:T] == 0)
+
+
+def test_joint_chunked_queries_row0(kc):
+    """The reference's hybrid schedule calls the operator on a chunk of query rows against all keys
+    (model.mm:404-510): Lq != Lk with q_row0 offsetting the tables."""
+    H, T, gh, gw = 2, 64, 12, 16
+    S = T + gh * gw
+    qkv, wq, wk, cos, sin = rand_case(61, 1, S, H, T, gh, gw)
+    want = oracle.joint_attention(qkv, 1, S, H, wq, wk, cos, sin)
+    ld = 3 * H * 128
+    x = dev_bits(qkv).view(-1)
+    o = torch.zeros((S, H * 128), dtype=torch.bfloat16, device="cuda")
+    dw = (dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin))
+    row0, rows = 100, 120
+    kc.joint_attention(x[row0 * ld:], x[H * 128:], x[2 * H * 128:], o[row0:], rows, S, H, ld, ld, ld, H * 128, *dw, 1e-6, 1, 0, row0)
+    kc.wait()
+    check(host_f32(o)[row0:row0 + rows], want[0, row0:row0 + rows], None, "chunked queries")
+    assert torch.all(o[:row0] == 0) and torch.all(o[row0 + rows:] == 0)
+
+
+def test_joint_caller_scratch_and_host_entry(kc):
+    H, T, gh, gw = 3, 32, 10, 10
+    S = T + gh * gw
+    qkv, wq, wk, cos, sin = rand_case(62, 2, S, H, T, gh, gw)
+    tl = np.array([20, 32], dtype=np.int32)
+    want = oracle.joint_attention(qkv, 2, S, H, wq, wk, cos, sin, text_len=tl, text_slots=T)
+    ld = 3 * H * 128
+    # caller-provided scratch
+    x = dev_bits(qkv).view(-1)
+    o = torch.zeros((2, S, H * 128), dtype=torch.bfloat16, device="cuda")
+    need = kc.joint_scratch_bytes(S, H, 1, 2)
+    scr = torch.empty(need, dtype=torch.uint8, device="cuda")
+    kc.joint_attention(x, x[H * 128:], x[2 * H * 128:], o, S, S, H, ld, ld, ld, H * 128, dev_f32(wq), dev_f32(wk), dev_f32(cos),
+                       dev_f32(sin), batch=2, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128,
+                       text_len=torch.from_numpy(tl).cuda(), text_slots=T, k_scratch=scr, k_scratch_bytes=need)
+    kc.wait()
+    check(host_f32(o), want, None, "caller scratch")
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.joint_attention(x, x[H * 128:], x[2 * H * 128:], o, S, S, H, ld, ld, ld, H * 128, dev_f32(wq), dev_f32(wk), dev_f32(cos),
+                           dev_f32(sin), batch=2, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, k_scratch=scr, k_scratch_bytes=need - 1)
+    assert e.value.code == binding.E_NOMEM
+    # host-pointer entry point: numpy in, numpy out
+    out = np.zeros((2, S, H * 128), dtype=np.uint16)
+    flat = qkv.reshape(-1)
+    kc.joint_attention_host(flat, flat[H * 128:], flat[2 * H * 128:], out, S, S, H, ld, ld, ld, H * 128, wq, wk, cos, sin,
+                            batch=2, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=tl, text_slots=T)
+    check(synth.bf16_bits_to_f32(out), want, None, "host entry")
+    assert np.array_equal(out.view(np.int16), o.view(torch.int16).cpu().numpy())    # same kernels, same bits
+
+
+def test_argument_errors_launch_nothing(kc):
+    n0 = kc.launches
+    t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")
+    f = torch.zeros(128 * 64, device="cuda")
+    bad = [
+        dict(heads=3, group=2),          # heads % group
+        dict(ldq=64),                    # ld < heads*128
+        dict(ldk=132),                   # not a multiple of 8
+    ]
+    for kw in bad:
+        a = dict(Lq=16, Lk=16, heads=1, ldq=128, ldk=128, ldv=128, ldo=128, group=1)
+        a.update(kw)
+        with pytest.raises(ops.KreaCudaError) as e:
+            kc.attention(t, t, t, t, a["Lq"], a["Lk"], a["heads"], a["ldq"], a["ldk"], a["ldv"], a["ldo"], a["group"])
+        assert e.value.code == binding.E_ARG
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.attention(t.view(-1)[1:], t, t, t, 16, 16, 1, 128, 128, 128, 128)   # misaligned pointer
+    assert e.value.code == binding.E_ARG
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.attention(t, t, t, t, 16, 16, 1, 128, 128, 128, 128, 1, True, 0)    # causal: not built, never silently wrong
+    assert e.value.code == binding.E_UNSUPPORTED
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.qk_norm_rope(t, f, f, f, f, 4, 128, 0, 1, 0, 0, 1e-6, 0, 5, None, None)   # big_dim without buffers (metal.mm:185)
+    assert e.value.code == binding.E_ARG
+    with pytest.raises(ops.KreaCudaError):
+        kc.qk_norm_rope(t, f, f, f, f, 4, 128, 64, 1, 0, 0, 1e-6)               # head does not fit in the row
+    assert kc.launches == n0
+    kc.attention(t, t, t, t, 0, 16, 1, 128, 128, 128, 128)                      # empty problems are fine
+    kc.wait()
+
+
+def test_no_visible_key_gives_zeros(kc):
+    """Every key padded away -> zeros, not NaN (attention.metal:316)."""
+    Lq, Lk = 130, 128
+    t = torch.randn(Lk, 128, device="cuda").to(torch.bfloat16)
+    o = torch.full((Lq, 128), 3.0, dtype=torch.bfloat16, device="cuda")
+    q = torch.randn(Lq, 128, device="cuda").to(torch.bfloat16)
+    tl = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc.attention(q, t, t, o, Lq, Lk, 1, 128, 128, 128, 128, text_len=tl, text_slots=128, q_row0=128)
+    kc.wait()
+    assert torch.all(o == 0)
+
+
+# ---------------------------------------------------------------------------------------------------
+def _golden_check(kc, name):
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    cfg = synth.CONFIGS[int(g["cid"])]
+    qkv = synth.qkv_slice(cfg)
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    tl = synth.text_lengths(cfg) if cfg.masked else None
+    got = run_joint(kc, qkv, cfg.batch, cfg.seq, cfg.heads, wq, wk, cos, sin, text_len=tl, text_slots=cfg.text if cfg.masked else 0)
+    got = got.reshape(cfg.batch, cfg.seq, cfg.heads, 128)
+    sel = np.stack([got[int(b), rows, int(h)] for b, h, rows in zip(g["sample"], g["head_of_block"], g["rows"])])
+    return cfg, qkv, (wq, wk, cos, sin, tl), got, check(sel, g["fp32"], g["ref"], name)
+
+
+def test_config0_full_tensor_and_golden(kc):
+    """512^2 joint attention (S = 1536, 24 heads): every output element against the oracle."""
+    cfg, qkv, (wq, wk, cos, sin, _), got, _ = _golden_check(kc, "c0_rows")
+    want = oracle.joint_attention(qkv, 1, cfg.seq, cfg.heads, wq, wk, cos, sin)
+    want_r = oracle.joint_attention(qkv, 1, cfg.seq, cfg.heads, wq, wk, cos, sin, ref_rounding=True)
+    rel, mx = check(got.reshape(1, cfg.seq, -1), want, want_r, "config 0 full")
+    print(f"config 0: rel-L2 {rel:.3e} max-abs {mx:.3e}")
+
+
+def test_config1_full_tensor_and_golden(kc):
+    """1024^2 joint attention (S = 4608, 24 heads), the headline configuration: full-tensor compare."""
+    cfg, qkv, (wq, wk, cos, sin, _), got, _ = _golden_check(kc, "c1_rows")
+    want = oracle.joint_attention(qkv, 1, cfg.seq, cfg.heads, wq, wk, cos, sin)
+    rel, mx = check(got.reshape(1, cfg.seq, -1), want, None, "config 1 full")
+    print(f"config 1: rel-L2 {rel:.3e} max-abs {mx:.3e}")
+    # size-independent properties: rows are convex combinations of V rows
+    v = synth.bf16_bits_to_f32(qkv[0, :, 2 * cfg.heads * 128:]).reshape(cfg.seq, cfg.heads, 128)
+    assert np.all(got[0] <= v.max(axis=0)[None] + 2e-2) and np.all(got[0] >= v.min(axis=0)[None] - 2e-2)
+
+
+def test_config2_masked_batch_golden_and_one_sample(kc):
+    """B=4 with text key-padding: golden rows of every sample, full compare of one sample, zero padded rows."""
+    cfg, qkv, (wq, wk, cos, sin, tl), got, _ = _golden_check(kc, "c2_rows")
+    b = 1
+    want = oracle.joint_attention(np.ascontiguousarray(qkv[b:b + 1]), 1, cfg.seq, cfg.heads, wq, wk, cos, sin,
+                                  text_len=tl[b:b + 1], text_slots=cfg.text, heads_sel=[0, 5, 13, 23])
+    for h in (0, 5, 13, 23):
+        check(got[b, :, h], want[0, :, h * 128:(h + 1) * 128], None, f"config 2 sample {b} head {h}")
+    for s in range(cfg.batch):
+        assert np.all(got[s, tl[s]:cfg.text] == 0)

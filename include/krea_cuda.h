@@ -55,7 +55,8 @@ KREA_CUDA_API krea_cuda* krea_cuda_create(int device, char* err, int errlen);
 KREA_CUDA_API void krea_cuda_destroy(krea_cuda* h);
 /* Message of the last failing call on this handle ("" if none). */
 KREA_CUDA_API const char* krea_cuda_last_error(krea_cuda* h);
-/* Use the caller's cudaStream_t (NULL = the handle's own stream, created by krea_cuda_create). */
+/* Enqueue on the caller's cudaStream_t from now on (NULL = the CUDA default stream).  A new handle
+ * starts on a private non-blocking stream of its own. */
 KREA_CUDA_API int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream);
 /* Wait for the stream (the counterpart of Metal::wait, engine/src/metal.h:57-58) and return
  * KREA_CUDA_E_DEVICE if any kernel since the last sync reported a timed-out wait. */

@@ -35,6 +35,17 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _check_register_budget(ptxas_log: str) -> None:
+    """The two-tile attention kernel re-balances registers between warpgroups with setmaxnreg: 8 warps go
+    up to 192 and 8 go down to 64, which only adds up (and can only be granted) if the CTA starts with
+    exactly 128 registers per thread.  A different launch count would leave the softmax warps waiting for
+    registers that never come, so refuse to build such a library."""
+    import re
+    for m in re.finditer(r"Compiling entry function '(\w*attn_fwd_sm100ILi2\w*)'.*?Used (\d+) registers", ptxas_log, re.S):
+        if int(m.group(2)) != 128:
+            raise RuntimeError(f"{m.group(1)} starts with {m.group(2)} registers per thread; setmaxnreg needs 128")
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
@@ -43,10 +54,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(OUT_DIR, src.replace(".cu", ".o"))
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
-        if verbose:
-            cmd.insert(1, "-Xptxas")
-            cmd.insert(2, "-v")
+        cmd = [_nvcc(), "-Xptxas", "-v", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
     for src, pr in procs:
@@ -55,6 +63,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out)
         if pr.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
+        _check_register_budget(out)
     cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs, "-cudart", "static"]
     subprocess.run(cmd, check=True)
     return LIB

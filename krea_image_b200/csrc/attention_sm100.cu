@@ -57,8 +57,11 @@ __device__ __forceinline__ void skip_range(int lo, int hi, int& first, int& end)
   if (end < first) end = first;
 }
 
-template <int NQ>
-__global__ void __launch_bounds__(NQ * 128 + 64, 1)
+// Thread layout: warps [0, 4*NQ) softmax warpgroups (one per query tile), then one warpgroup whose
+// warp 0 is the TMA producer and warp 1 the MMA issuer.  The softmax warpgroups take registers from
+// the others with setmaxnreg.  EMU: how many of every four element pairs use the polynomial exp2.
+template <int NQ, int EMU>
+__global__ void __launch_bounds__(NQ * 128 + 128 + (NQ == 2 ? 128 : 0), 1)
 attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle needs
@@ -111,7 +114,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     abort_word[1] = 0u;                                                     // private word of the drain loop
     fence_mbar_init();
   }
-  if (warp == NQ * 4 + 1) {
+  if (warp == NQ * 4 + 1) {   // the MMA warp owns the TMEM allocation
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -120,8 +123,10 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  constexpr int WARP_TMA = NQ * 4, WARP_MMA = NQ * 4 + 1;
   if (warp < NQ * 4) {
     // =============================== softmax / epilogue warpgroups ===============================
+    if constexpr (NQ == 2) reg_inc<192>();   // 8 warps x 192 + 8 warps x 64 = the 128 per thread the CTA starts with
     const int g = warp >> 2;
     const int r = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
     const int row = q0 + g * BM + r;
@@ -132,67 +137,75 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (tile_active && n_tiles > 0) {
       // ---- stage Q (with the fused RMSNorm + RoPE prologue when weights are given) ----
+      // Pass 1 copies the raw row into its swizzled place (16-byte chunk c of row r goes to chunk slot
+      // c ^ (r & 7) of the row's 128 B line) while summing squares; pass 2 normalises and rotates in
+      // place, one chunk (pair of chunks for rotate-half) at a time so that few registers are live.
       {
         const int rc = min(row, p.Lq - 1);               // rows past Lq are clamped, never stored
         const uint4* src = (const uint4*)(p.Q + (size_t)b * p.bsq + (size_t)rc * p.ldq + (size_t)h * D);
-        uint4 raw[16];
-#pragma unroll
-        for (int c = 0; c < 16; c++) raw[c] = __ldg(src + c);
         uint8_t* qdst = q_smem + g * TILE_BYTES + r * 128;
-        if (p.wq != nullptr) {
-          float ss = 0.f;
+        auto slot = [&](int c) { return (uint4*)(qdst + (c >> 3) * HALF_BYTES + (((c & 7) ^ (r & 7)) << 4)); };
+        float ss = 0.f;
+#pragma unroll 4
+        for (int c = 0; c < 16; c++) {
+          const uint4 v = __ldg(src + c);
+          *slot(c) = v;
+          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int c = 0; c < 16; c++) {
-            const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              const float a = bf16lo_to_f32(w4[e]), bb = bf16hi_to_f32(w4[e]);
-              ss = fmaf(a, a, ss);
-              ss = fmaf(bb, bb, ss);
-            }
+          for (int e = 0; e < 4; e++) {
+            const float x0 = bf16lo_to_f32(w4[e]), x1 = bf16hi_to_f32(w4[e]);
+            ss = fmaf(x0, x0, ss);
+            ss = fmaf(x1, x1, ss);
           }
+        }
+        if (p.wq != nullptr) {
           const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
           const int pos = p.q_row0 + rc;
           const float4* cr = (const float4*)(p.cos + (size_t)pos * 64);
           const float4* sr = (const float4*)(p.sin + (size_t)pos * 64);
           const float4* wv = (const float4*)p.wq;
           if (p.rope_mode == 1) {
-            // rotate-half: channel i pairs with i + 64 (norm.metal:114-126); chunk c pairs with chunk c + 8
-#pragma unroll
+            // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), i.e. chunk c with chunk c + 8
+#pragma unroll 1
             for (int c = 0; c < 8; c++) {
-              const uint32_t lo4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
-              const uint32_t hi4[4] = {raw[c + 8].x, raw[c + 8].y, raw[c + 8].z, raw[c + 8].w};
-              float xl[8], xh[8], cs[8], sn[8];
-              const float4 wl0 = __ldg(wv + 2 * c), wl1 = __ldg(wv + 2 * c + 1);
-              const float4 wh0 = __ldg(wv + 16 + 2 * c), wh1 = __ldg(wv + 16 + 2 * c + 1);
-              const float wl[8] = {wl0.x, wl0.y, wl0.z, wl0.w, wl1.x, wl1.y, wl1.z, wl1.w};
-              const float wh[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
-              const float4 c0 = __ldg(cr + 2 * c), c1 = __ldg(cr + 2 * c + 1), s0 = __ldg(sr + 2 * c), s1 = __ldg(sr + 2 * c + 1);
-              const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-              const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+              const uint4 lo = *slot(c), hi = *slot(c + 8);
+              const uint32_t lo4[4] = {lo.x, lo.y, lo.z, lo.w}, hi4[4] = {hi.x, hi.y, hi.z, hi.w};
+              uint32_t ol[4], oh[4];
 #pragma unroll
-              for (int e = 0; e < 4; e++) {
-                xl[2 * e] = bf16lo_to_f32(lo4[e]) * rrms * wl[2 * e];
-                xl[2 * e + 1] = bf16hi_to_f32(lo4[e]) * rrms * wl[2 * e + 1];
-                xh[2 * e] = bf16lo_to_f32(hi4[e]) * rrms * wh[2 * e];
-                xh[2 * e + 1] = bf16hi_to_f32(hi4[e]) * rrms * wh[2 * e + 1];
-              }
+              for (int hf = 0; hf < 2; hf++) {
+                const float4 wl = __ldg(wv + 2 * c + hf), wh = __ldg(wv + 16 + 2 * c + hf);
+                const float4 cc = __ldg(cr + 2 * c + hf), sc = __ldg(sr + 2 * c + hf);
+                const float wlf[4] = {wl.x, wl.y, wl.z, wl.w}, whf[4] = {wh.x, wh.y, wh.z, wh.w};
+                const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
+                float yl[4], yh[4];
 #pragma unroll
-              for (int e = 0; e < 8; e++) {
-                cs[e] = xl[e] * cc[e] - xh[e] * sc[e];
-                sn[e] = xh[e] * cc[e] + xl[e] * sc[e];
+                for (int e = 0; e < 2; e++) {
+                  const uint32_t a = lo4[2 * hf + e], bb = hi4[2 * hf + e];
+                  const float xl0 = bf16lo_to_f32(a) * rrms * wlf[2 * e], xl1 = bf16hi_to_f32(a) * rrms * wlf[2 * e + 1];
+                  const float xh0 = bf16lo_to_f32(bb) * rrms * whf[2 * e], xh1 = bf16hi_to_f32(bb) * rrms * whf[2 * e + 1];
+                  yl[2 * e] = xl0 * cf[2 * e] - xh0 * sf[2 * e];
+                  yl[2 * e + 1] = xl1 * cf[2 * e + 1] - xh1 * sf[2 * e + 1];
+                  yh[2 * e] = xh0 * cf[2 * e] + xl0 * sf[2 * e];
+                  yh[2 * e + 1] = xh1 * cf[2 * e + 1] + xl1 * sf[2 * e + 1];
+                }
+                ol[2 * hf] = pack_bf16x2(yl[0], yl[1]);
+                ol[2 * hf + 1] = pack_bf16x2(yl[2], yl[3]);
+                oh[2 * hf] = pack_bf16x2(yh[0], yh[1]);
+                oh[2 * hf + 1] = pack_bf16x2(yh[2], yh[3]);
               }
-              raw[c] = make_uint4(pack_bf16x2(cs[0], cs[1]), pack_bf16x2(cs[2], cs[3]), pack_bf16x2(cs[4], cs[5]), pack_bf16x2(cs[6], cs[7]));
-              raw[c + 8] = make_uint4(pack_bf16x2(sn[0], sn[1]), pack_bf16x2(sn[2], sn[3]), pack_bf16x2(sn[4], sn[5]), pack_bf16x2(sn[6], sn[7]));
+              *slot(c) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+              *slot(c + 8) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
             }
           } else {
-#pragma unroll
+            const bool rot = p.rope_mode == 0;   // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113)
+#pragma unroll 1
             for (int c = 0; c < 16; c++) {
-              const uint32_t w4[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+              const uint4 v = *slot(c);
+              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
               const float4 wa = __ldg(wv + 2 * c), wb = __ldg(wv + 2 * c + 1);
               const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
               float4 cc = make_float4(1.f, 1.f, 1.f, 1.f), sc = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.rope_mode == 0) {  // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113)
+              if (rot) {
                 cc = __ldg(cr + c);
                 sc = __ldg(sr + c);
               }
@@ -204,15 +217,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const float x1 = bf16hi_to_f32(w4[e]) * rrms * ww[2 * e + 1];
                 o4[e] = pack_bf16x2(x0 * cf[e] - x1 * sf[e], x0 * sf[e] + x1 * cf[e]);
               }
-              raw[c] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+              *slot(c) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
             }
           }
-        }
-        // 128-byte swizzle: 16-byte chunk c of row r lands in chunk slot c ^ (r & 7) of its 128 B row
-#pragma unroll
-        for (int c = 0; c < 16; c++) {
-          uint8_t* dst = qdst + (c >> 3) * HALF_BYTES + (((c & 7) ^ (r & 7)) << 4);
-          *(uint4*)dst = raw[c];
         }
         fence_proxy_async_smem();
         mbar_arrive(&q_ready[g]);
@@ -243,45 +250,73 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             s[c] = ok ? s[c] : -INFINITY;
           }
         }
-        float mx = s[0];
+        // row max: four independent chains of 3-input max
+        float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-        for (int c = 1; c < 128; c++) mx = fmaxf(mx, s[c]);
-        const float lm = mx * sc2;
+        for (int c = 4; c < 128; c += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; u++) mx4[u] = max3(mx4[u], s[c + 2 * u], s[c + 2 * u + 1]);
+        }
+        const float lm = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
         const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
+        bool rescale = false;                   // warp-uniform
+        float o_alpha = 1.f;
         if (__any_sync(0xffffffffu, need)) {
           const float m_new = need ? lm : m_i;
           const float alpha = (m_i == -INFINITY) ? 0.f : ex2_approx(m_i - m_new);
           m_i = m_new;
           l_i *= alpha;
-          if (j > 0) {
-            // rescale this row of O; P V of the previous tile must have landed first
-            mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
-            tc_fence_after();
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
-              uint32_t ov[32];
-              tmem_ld32(tO + c0, ov);
-              tmem_wait_ld();
-#pragma unroll
-              for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
-              tmem_st32(tO + c0, ov);
-            }
-            tmem_wait_st();
-          }
+          rescale = j > 0;
+          o_alpha = alpha;
         }
         const float m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
-        uint32_t pk[64];
-        float lsum = 0.f;
+        // p = exp2(s * scale_log2 - m): packed fp32x2 arithmetic; EMU of every 4 pairs take the
+        // polynomial exp2 on the FMA pipe instead of the (16/clk/SM) special-function unit
+        const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm2 = pack_f32x2(-m_use, -m_use);
+        uint64_t lsum2[2] = {0ull, 0ull};
 #pragma unroll
-        for (int c = 0; c < 128; c += 2) {
-          const float p0 = ex2_approx(fmaf(s[c], sc2, -m_use));
-          const float p1 = ex2_approx(fmaf(s[c + 1], sc2, -m_use));
-          lsum += p0 + p1;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
+        for (int ch = 0; ch < 4; ch++) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            const int c = ch * 32 + 2 * i;
+            const uint64_t x2 = fma_f32x2(pack_f32x2(s[c], s[c + 1]), sc2x2, negm2);
+            uint64_t p2;
+            if ((i & 3) < EMU) {
+              p2 = exp2_emulated_x2(x2);
+            } else {
+              float x0, x1;
+              unpack_f32x2(x2, x0, x1);
+              p2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+            }
+            lsum2[i & 1] = add_f32x2(lsum2[i & 1], p2);
+            float p0, p1;
+            unpack_f32x2(p2, p0, p1);
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(tS + ch * 16, pk);
         }
-        l_i += lsum;
-        tmem_st32(tS + 0, pk);
-        tmem_st32(tS + 32, pk + 32);
+        {
+          float a0, a1, b0, b1;
+          unpack_f32x2(lsum2[0], a0, a1);
+          unpack_f32x2(lsum2[1], b0, b1);
+          l_i += (a0 + a1) + (b0 + b1);
+        }
+        if (rescale) {
+          // the running max moved: rescale this row of O before P V of this tile may accumulate into it
+          // (P V of the previous tile must have landed first)
+          mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t ov[32];
+            tmem_ld32(tO + c0, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * o_alpha);
+            tmem_st32(tO + c0, ov);
+          }
+        }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&p_full[g]);
@@ -327,7 +362,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
       for (int c = 0; c < 16; c++) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     }
-  } else if (warp == NQ * 4) {
+  } else {
+    if constexpr (NQ == 2) reg_dec<64>();
+    if (warp == WARP_TMA) {
     // ======================================= TMA producer =======================================
     if (lane == 0 && n_tiles > 0) {
       tma_prefetch_desc(&tmK);
@@ -354,7 +391,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           mbar_wait_slow(&kv_full[n % NSTAGE], (n / NSTAGE) & 1, abort_word + 1, SITE_DRAIN);
       }
     }
-  } else {
+    } else if (warp == WARP_MMA) {
     // ======================================== MMA issuer ========================================
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
@@ -408,6 +445,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (*abort_word != 0u) break;
       }
     }
+    }
   }
 
   tc_fence_before();
@@ -422,24 +460,30 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   }
 }
 
-template <int NQ>
+template <int NQ, int EMU>
 static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, cudaStream_t stream) {
   const int smem = SmemLayout<NQ>::total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<NQ, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   dim3 grid((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
-  attn_fwd_sm100<NQ><<<grid, NQ * 128 + 64, smem, stream>>>(tmK, tmV, p);
+  attn_fwd_sm100<NQ, EMU><<<grid, NQ * 128 + 128 + (NQ == 2 ? 128 : 0), smem, stream>>>(tmK, tmV, p);
   return cudaGetLastError();
 }
 
-cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int nq, cudaStream_t stream) {
-  return nq == 1 ? launch_impl<1>(tmK, tmV, p, stream) : launch_impl<2>(tmK, tmV, p, stream);
+cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int nq, int emu, cudaStream_t stream) {
+  if (nq == 1) return launch_impl<1, 0>(tmK, tmV, p, stream);
+  switch (emu) {
+    case 0: return launch_impl<2, 0>(tmK, tmV, p, stream);
+    case 2: return launch_impl<2, 2>(tmK, tmV, p, stream);
+    case 3: return launch_impl<2, 3>(tmK, tmV, p, stream);
+    default: return launch_impl<2, 1>(tmK, tmV, p, stream);
+  }
 }
 
 }  // namespace krea

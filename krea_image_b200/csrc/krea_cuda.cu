@@ -37,6 +37,7 @@ struct krea_cuda {
   uint64_t launches = 0;
   PFN_encodeTiled encode = nullptr;
   int nq = 2;                       // query tiles per CTA
+  int emu = 1;                      // of every 4 element pairs, how many take the polynomial exp2
   bool profiling = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
   std::vector<cudaEvent_t> event_pool;
@@ -131,9 +132,13 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     return nullptr;
   }
   h->stream = h->own_stream;
-  if (const char* s = getenv("KREA_CUDA_NQ")) {  // debugging knob: 1 or 2 query tiles per CTA
+  if (const char* s = getenv("KREA_CUDA_NQ")) {  // tuning knob: 1 or 2 query tiles per CTA
     const int v = atoi(s);
     if (v == 1 || v == 2) h->nq = v;
+  }
+  if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
+    const int v = atoi(s);
+    if (v >= 0 && v <= 3) h->emu = v;
   }
   return h;
 }
@@ -161,7 +166,7 @@ const char* krea_cuda_last_error(krea_cuda* h) { return h ? h->err.c_str() : "nu
 
 int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream) {
   if (!h) return KREA_CUDA_E_ARG;
-  h->stream = cuda_stream ? (cudaStream_t)cuda_stream : h->own_stream;
+  h->stream = (cudaStream_t)cuda_stream;
   return KREA_CUDA_OK;
 }
 
@@ -331,7 +336,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   int nq = h->nq;
   {
     ProfileMark pm(h, 1);
-    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->stream));
+    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->emu, h->stream));
   }
   h->launches++;
   return KREA_CUDA_OK;

@@ -52,7 +52,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site) {
+static __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -174,6 +174,60 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 // The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// ---- register re-balancing between warpgroups ------------------------------------------------------
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// ---- packed fp32x2 arithmetic (one instruction, two lanes) -------------------------------------------
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// 2^x for two lanes on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5];
+// 2^f by a degree-3 polynomial (max relative error 7.5e-5, far below bf16 resolution), 2^n by adding
+// n to the exponent field.  Valid for -126 <= x <= 126; smaller x is clamped (result ~1e-38).
+__device__ __forceinline__ uint64_t exp2_emulated_x2(uint64_t x2) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t x = pack_f32x2(x0, x1);
+  const uint64_t magic = pack_f32x2(12582912.0f, 12582912.0f);       // 1.5 * 2^23: rounds to integer
+  const uint64_t t = add_f32x2(x, magic);
+  const uint64_t n = add_f32x2(t, pack_f32x2(-12582912.0f, -12582912.0f));
+  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.0f, -1.0f), x);
+  uint64_t q = fma_f32x2(pack_f32x2(0.05517162f, 0.05517162f), f, pack_f32x2(0.24261113f, 0.24261113f));
+  q = fma_f32x2(q, f, pack_f32x2(0.69326097f, 0.69326097f));
+  q = fma_f32x2(q, f, pack_f32x2(0.99992806f, 0.99992806f));
+  float t0, t1, q0, q1;
+  unpack_f32x2(t, t0, t1);
+  unpack_f32x2(q, q0, q1);
+  const float r0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  const float r1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+  return pack_f32x2(r0, r1);
 }
 
 // ---- small math helpers ----------------------------------------------------------------------------

@@ -61,8 +61,8 @@ class KreaCuda:
 
     # ---- stream handling --------------------------------------------------------------------------
     def set_stream(self, stream):
-        """stream: a torch.cuda.Stream, a raw cudaStream_t address, or None for the handle's own."""
-        s = None if stream is None else getattr(stream, "cuda_stream", stream)
+        """stream: a torch.cuda.Stream or a raw cudaStream_t address (0 / None = the CUDA default stream)."""
+        s = None if stream is None else (getattr(stream, "cuda_stream", stream) or None)
         self._check(self.lib.krea_cuda_set_stream(self.h, s))
 
     def wait(self):

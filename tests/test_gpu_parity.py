@@ -16,7 +16,10 @@ pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 REL_L2_TOL = 5e-3     # vs fp32 oracle
 MAX_ABS_TOL = 2e-2    # vs fp32 oracle
-REL_L2_REF = 2.5e-3   # vs the oracle run with the reference's roundings
+# vs the oracle run with the reference's roundings.  Not tighter than the fp32 bound by much: P is rounded to
+# bf16 relative to a lazily updated running max (as in the reference, attention.metal:33-36), so the
+# rounding noise of the two computations is independent even where the math is identical.
+REL_L2_REF = 4e-3
 
 
 @pytest.fixture(scope="module")

@@ -398,25 +398,34 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, true);
       bool active[NQ];
       for (int g = 0; g < NQ; g++) active[g] = (q0 + g * BM) < p.Lq;
-      const uint32_t q_base = smem_u32(q_smem), kv_base = smem_u32(kv_smem);
+      // The issuing thread is alone in its warp, so every instruction between two MMAs costs its full
+      // latency.  Descriptors are therefore assembled from precomputed 32-bit halves: the high word is
+      // a constant per operand kind, the low word is (address >> 4) plus a compile-time step.
+      constexpr uint32_t HI = desc_hi(1024);                          // sbo = 1024 B for every operand here
+      constexpr uint32_t LBO_K = (16u >> 4) << 16;                    // K-major: lbo unused
+      constexpr uint32_t LBO_V = ((uint32_t)HALF_BYTES >> 4) << 16;   // MN-major V: next 64 channels 16 KB away
+      const uint32_t q_lo = (smem_u32(q_smem) >> 4) | LBO_K;
+      const uint32_t kv_lo = smem_u32(kv_smem) >> 4;
+      constexpr uint32_t TILE16 = TILE_BYTES >> 4, HALF16 = HALF_BYTES >> 4;
 
       auto issue_qk = [&](int g, int stage) {
-        const uint32_t qa = q_base + g * TILE_BYTES, kb = kv_base + stage * TILE_BYTES;
+        const uint32_t qa = q_lo + g * TILE16, kb = (kv_lo + stage * TILE16) | LBO_K;
 #pragma unroll
         for (int k = 0; k < 8; k++) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          umma_ss(tmem_base + g * BN, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(kb + off, 16, 1024), idesc_qk, k > 0);
+          const uint32_t off = (k >> 2) * HALF16 + (k & 3) * 2;       // 16 channels = 32 B per step inside a 128 B row
+          if (k == 0) umma_ss<false>(tmem_base + g * BN, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
+          else umma_ss<true>(tmem_base + g * BN, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
         }
         umma_commit(&s_full[g]);
       };
       auto issue_pv = [&](int g, int stage, bool first) {
-        const uint32_t vb = kv_base + stage * TILE_BYTES;
+        const uint32_t vb = (kv_lo + stage * TILE16) | LBO_V;
+        const uint32_t d_o = tmem_base + NQ * BN + g * D, a_p = tmem_base + g * BN;
+        // 16 keys per MMA: A = 8 packed-bf16 columns of P in TMEM, B = 16 rows (2048 B) of the V stage
+        if (first) umma_ts<false>(d_o, a_p, make_desc(vb, HI), idesc_pv);
+        else umma_ts<true>(d_o, a_p, make_desc(vb, HI), idesc_pv);
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          // 16 keys per MMA: A = 8 packed-bf16 columns of P in TMEM, B = 16 rows (2048 B) of the V stage
-          umma_ts(tmem_base + NQ * BN + g * D, tmem_base + g * BN + k * 8, umma_smem_desc(vb + k * 2048, HALF_BYTES, 1024), idesc_pv,
-                  (!first || k > 0) ? 1u : 0u);
-        }
+        for (int k = 1; k < 8; k++) umma_ts<true>(d_o, a_p + k * 8, make_desc(vb + k * 128, HI), idesc_pv);
         umma_commit(&pv_done[g]);
       };
 

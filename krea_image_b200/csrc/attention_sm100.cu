@@ -26,6 +26,15 @@
 #include "attention_sm100.h"
 #include "sm100_ptx.cuh"
 
+// Optional phase trace for tuning builds (-DKREA_ATTN_TRACE): CTA 0 records clock64() at the points
+// marked KTRACE into p.trace; compiled out otherwise.
+#ifdef KREA_ATTN_TRACE
+#define KTRACE(cond, slot, j) \
+  do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.trace && (j) < 64) p.trace[(slot) * 64 + (j)] = clock64(); } while (0)
+#else
+#define KTRACE(cond, slot, j) do { } while (0)
+#endif
+
 namespace krea {
 
 constexpr int D = 128;               // head_dim
@@ -232,14 +241,17 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       for (int j = 0; j < n_tiles; j++) {
         const int kt = tile_of(j);
         const int key0 = kt * BN;
+        KTRACE(threadIdx.x == g * 128, g * 8 + 0, j);
         mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
         tc_fence_after();
+        KTRACE(threadIdx.x == g * 128, g * 8 + 1, j);
         uint32_t sv[128];
         tmem_ld32(tS + 0, sv + 0);
         tmem_ld32(tS + 32, sv + 32);
         tmem_ld32(tS + 64, sv + 64);
         tmem_ld32(tS + 96, sv + 96);
         tmem_wait_ld();
+        KTRACE(threadIdx.x == g * 128, g * 8 + 2, j);
         float* s = (float*)sv;
         const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
         if (need_mask) {
@@ -259,6 +271,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         const float lm = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
         const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
+        KTRACE(threadIdx.x == g * 128, g * 8 + 3, j);
         bool rescale = false;                   // warp-uniform
         float o_alpha = 1.f;
         if (__any_sync(0xffffffffu, need)) {
@@ -302,6 +315,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           unpack_f32x2(lsum2[1], b0, b1);
           l_i += (a0 + a1) + (b0 + b1);
         }
+        KTRACE(threadIdx.x == g * 128, g * 8 + 4, j);
         if (rescale) {
           // the running max moved: rescale this row of O before P V of this tile may accumulate into it
           // (P V of the previous tile must have landed first)
@@ -318,6 +332,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           }
         }
         tmem_wait_st();
+        KTRACE(threadIdx.x == g * 128, g * 8 + 5, j);
         tc_fence_before();
         mbar_arrive(&p_full[g]);
       }
@@ -444,10 +459,13 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (has_next) mbar_wait(&kv_full[nk % NSTAGE], (nk / NSTAGE) & 1, abort_word, SITE_KV_FULL);
         for (int g = 0; g < NQ; g++) {
           if (!active[g]) continue;
+          KTRACE(true, 16 + g * 4 + 0, j);
           mbar_wait(&p_full[g], j & 1, abort_word, SITE_P);
           tc_fence_after();
+          KTRACE(true, 16 + g * 4 + 1, j);
           issue_pv(g, nv % NSTAGE, j == 0);
           if (has_next) issue_qk(g, nk % NSTAGE);
+          KTRACE(true, 16 + g * 4 + 2, j);
         }
         umma_commit(&kv_empty[nv % NSTAGE]);
         if (has_next) umma_commit(&kv_empty[nk % NSTAGE]);

@@ -28,6 +28,7 @@ struct AttnParams {
   const int32_t* text_len;
   int text_slots;
   uint32_t* status;            // device word: 0 = ok, else (site | qblk << 8 | head << 20) of a timed-out wait
+  long long* trace;            // tuning builds only (KREA_ATTN_TRACE): clock64 samples of CTA 0, else nullptr
 };
 
 // K and V are described by 3-D tensor maps (column, row, sample) with 64-column x 128-row boxes and

@@ -53,8 +53,8 @@ struct SmemLayout {
   static constexpr int q_off = 0;
   static constexpr int kv_off = NQ * TILE_BYTES;
   static constexpr int bar_off = kv_off + NSTAGE * TILE_BYTES;
-  // barriers: q_ready[NQ], s_full[NQ], p_full[NQ], pv_done[NQ], kv_full[NSTAGE], kv_empty[NSTAGE]
-  static constexpr int n_bars = 4 * NQ + 2 * NSTAGE;
+  // barriers: q_ready[NQ], s_full[NQ], p_full[NQ], pv_done[NQ], kv_full[NSTAGE], kv_empty[NSTAGE], s_free
+  static constexpr int n_bars = 4 * NQ + 2 * NSTAGE + 1;
   static constexpr int misc_off = bar_off + n_bars * 8;
   static constexpr int total = misc_off + 16;
 };
@@ -85,6 +85,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   uint64_t* pv_done = bars + 3 * NQ;
   uint64_t* kv_full = bars + 4 * NQ;
   uint64_t* kv_empty = kv_full + NSTAGE;
+  uint64_t* s_free = kv_empty + NSTAGE;
   uint32_t* tmem_slot = (uint32_t*)(smem + L::misc_off);
   volatile uint32_t* abort_word = (volatile uint32_t*)(smem + L::misc_off + 4);
 
@@ -107,7 +108,15 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const int n_tiles = nkt_all - (skip_end - skip_first);
   auto tile_of = [&](int j) { return j < skip_first ? j : j + (skip_end - skip_first); };
 
-  constexpr uint32_t TMEM_COLS = NQ * 256;
+  // Tensor memory map (512 columns x 128 lanes x 32 bit):
+  //   [  0,128)  S     the ONE score tile, shared by the query tiles in turn: it is occupied only from the
+  //                    end of a Q K^T product until the owning warpgroup has copied it to registers
+  //   [128,256)  P_g   bf16 probabilities of tile g (64 columns each), the A operand of P V
+  //   [256,512)  O_g   fp32 output accumulators (128 columns each)
+  // Keeping P out of the S columns removes the dependency "next Q K^T of a tile waits for its P V", so
+  // each softmax warpgroup always finds its next score tile ready and the tensor pipe never drains.
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_S = 0, COL_P = 128, COL_O = 256;
   if (threadIdx.x == 0) {
     for (int g = 0; g < NQ; g++) {
       mbar_init(&q_ready[g], 128);
@@ -119,6 +128,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
+    mbar_init(s_free, 128);
     abort_word[0] = (p.status != nullptr && *p.status != 0u) ? 0xFFu : 0u;  // a failed launch poisons later CTAs
     abort_word[1] = 0u;                                                     // private word of the drain loop
     fence_mbar_init();
@@ -141,8 +151,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const int row = q0 + g * BM + r;
     const bool tile_active = (q0 + g * BM) < p.Lq;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t tS = lane_addr + (uint32_t)(g * BN);
-    const uint32_t tO = lane_addr + (uint32_t)(NQ * BN + g * D);
+    const uint32_t tS = lane_addr + COL_S;
+    const uint32_t tP = lane_addr + COL_P + (uint32_t)(g * 64);
+    const uint32_t tO = lane_addr + COL_O + (uint32_t)(g * D);
 
     if (tile_active && n_tiles > 0) {
       // ---- stage Q (with the fused RMSNorm + RoPE prologue when weights are given) ----
@@ -251,6 +262,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         tmem_ld32(tS + 64, sv + 64);
         tmem_ld32(tS + 96, sv + 96);
         tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(s_free);     // the scores are in registers: the next Q K^T may overwrite the tile
         KTRACE(threadIdx.x == g * 128, g * 8 + 2, j);
         float* s = (float*)sv;
         const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
@@ -283,6 +296,11 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           o_alpha = alpha;
         }
         const float m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
+        if (j > 0) {
+          // P V of the previous key tile still reads P_g (and, for a rescale, writes O_g) until this completes
+          mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+          tc_fence_after();
+        }
         // p = exp2(s * scale_log2 - m): packed fp32x2 arithmetic; EMU of every 4 pairs take the
         // polynomial exp2 on the FMA pipe instead of the (16/clk/SM) special-function unit
         const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm2 = pack_f32x2(-m_use, -m_use);
@@ -307,7 +325,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             unpack_f32x2(p2, p0, p1);
             pk[i] = pack_bf16x2(p0, p1);
           }
-          tmem_st16(tS + ch * 16, pk);
+          tmem_st16(tP + ch * 16, pk);
         }
         {
           float a0, a1, b0, b1;
@@ -318,9 +336,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         KTRACE(threadIdx.x == g * 128, g * 8 + 4, j);
         if (rescale) {
           // the running max moved: rescale this row of O before P V of this tile may accumulate into it
-          // (P V of the previous tile must have landed first)
-          mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
-          tc_fence_after();
+          // (P V of the previous tile has landed: see the wait above)
 #pragma unroll
           for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t ov[32];
@@ -408,7 +424,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     } else if (warp == WARP_MMA) {
     // ======================================== MMA issuer ========================================
-    if (lane == 0 && n_tiles > 0) {
+    // The whole warp runs this code converged; one elected lane issues the MMAs and commits.
+    if (n_tiles > 0) {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, true);
       bool active[NQ];
@@ -425,50 +443,79 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
       auto issue_qk = [&](int g, int stage) {
         const uint32_t qa = q_lo + g * TILE16, kb = (kv_lo + stage * TILE16) | LBO_K;
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          const uint32_t off = (k >> 2) * HALF16 + (k & 3) * 2;       // 16 channels = 32 B per step inside a 128 B row
-          if (k == 0) umma_ss<false>(tmem_base + g * BN, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
-          else umma_ss<true>(tmem_base + g * BN, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
+          for (int k = 0; k < 8; k++) {
+            const uint32_t off = (k >> 2) * HALF16 + (k & 3) * 2;     // 16 channels = 32 B per step inside a 128 B row
+            if (k == 0) umma_ss<false>(tmem_base + COL_S, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
+            else umma_ss<true>(tmem_base + COL_S, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
+          }
+          umma_commit(&s_full[g]);
         }
-        umma_commit(&s_full[g]);
+        __syncwarp();
       };
       auto issue_pv = [&](int g, int stage, bool first) {
         const uint32_t vb = (kv_lo + stage * TILE16) | LBO_V;
-        const uint32_t d_o = tmem_base + NQ * BN + g * D, a_p = tmem_base + g * BN;
+        const uint32_t d_o = tmem_base + COL_O + g * D, a_p = tmem_base + COL_P + g * 64;
         // 16 keys per MMA: A = 8 packed-bf16 columns of P in TMEM, B = 16 rows (2048 B) of the V stage
-        if (first) umma_ts<false>(d_o, a_p, make_desc(vb, HI), idesc_pv);
-        else umma_ts<true>(d_o, a_p, make_desc(vb, HI), idesc_pv);
+        if (leader) {
+          if (first) umma_ts<false>(d_o, a_p, make_desc(vb, HI), idesc_pv);
+          else umma_ts<true>(d_o, a_p, make_desc(vb, HI), idesc_pv);
 #pragma unroll
-        for (int k = 1; k < 8; k++) umma_ts<true>(d_o, a_p + k * 8, make_desc(vb + k * 128, HI), idesc_pv);
-        umma_commit(&pv_done[g]);
+          for (int k = 1; k < 8; k++) umma_ts<true>(d_o, a_p + k * 8, make_desc(vb + k * 128, HI), idesc_pv);
+          umma_commit(&pv_done[g]);
+        }
+        __syncwarp();
       };
 
+      // Issue order: Q K^T of a tile is issued as soon as the shared S tile is free (the other
+      // warpgroup has copied its scores out), ahead of the P V that consumes the same tile's previous
+      // probabilities, so the tensor pipe always has the next score tile in flight.
+      uint32_t nqk = 0;        // Q K^T products issued so far == S-tile hand-overs requested
+      auto wait_s_free = [&]() {
+        if (nqk > 0) {
+          mbar_wait(s_free, (nqk - 1) & 1, abort_word, SITE_S);
+          tc_fence_after();
+        }
+        nqk++;
+      };
       for (int g = 0; g < NQ; g++)
         if (active[g]) mbar_wait(&q_ready[g], 0, abort_word, SITE_Q);
       mbar_wait(&kv_full[0], 0, abort_word, SITE_KV_FULL);   // K_0
       tc_fence_after();
       for (int g = 0; g < NQ; g++)
-        if (active[g]) issue_qk(g, 0);
-      umma_commit(&kv_empty[0]);
+        if (active[g]) {
+          wait_s_free();
+          issue_qk(g, 0);
+        }
+      if (leader) umma_commit(&kv_empty[0]);
 
       for (int j = 0; j < n_tiles; j++) {
         const int nv = 2 * j + 1, nk = 2 * j + 2;
         const bool has_next = j + 1 < n_tiles;
-        mbar_wait(&kv_full[nv % NSTAGE], (nv / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        KTRACE(lane == 0, 24, j);
         if (has_next) mbar_wait(&kv_full[nk % NSTAGE], (nk / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        mbar_wait(&kv_full[nv % NSTAGE], (nv / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        KTRACE(lane == 0, 25, j);
         for (int g = 0; g < NQ; g++) {
           if (!active[g]) continue;
-          KTRACE(true, 16 + g * 4 + 0, j);
+          if (has_next) {
+            wait_s_free();
+            KTRACE(lane == 0, 16 + g * 4 + 0, j);
+            issue_qk(g, nk % NSTAGE);
+          }
+          KTRACE(lane == 0, 16 + g * 4 + 1, j);
           mbar_wait(&p_full[g], j & 1, abort_word, SITE_P);
           tc_fence_after();
-          KTRACE(true, 16 + g * 4 + 1, j);
+          KTRACE(lane == 0, 16 + g * 4 + 2, j);
           issue_pv(g, nv % NSTAGE, j == 0);
-          if (has_next) issue_qk(g, nk % NSTAGE);
-          KTRACE(true, 16 + g * 4 + 2, j);
+          KTRACE(lane == 0, 16 + g * 4 + 3, j);
         }
-        umma_commit(&kv_empty[nv % NSTAGE]);
-        if (has_next) umma_commit(&kv_empty[nk % NSTAGE]);
+        if (leader) {
+          umma_commit(&kv_empty[nv % NSTAGE]);
+          if (has_next) umma_commit(&kv_empty[nk % NSTAGE]);
+        }
+        __syncwarp();
         if (*abort_word != 0u) break;
       }
     }

@@ -85,6 +85,15 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       : "memory");
 }
 
+// True in exactly one lane of a fully converged warp.  The MMA warp runs its whole loop converged and
+// only predicates the asynchronous instructions on this, so that descriptor arithmetic and barrier
+// polling stay on the warp-uniform datapath instead of a divergent single-lane path.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- tensor memory ---------------------------------------------------------------------------------
 // One full warp allocates; the base address (lane 0, column base) is written to *smem_slot.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {

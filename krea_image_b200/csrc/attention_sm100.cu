@@ -23,6 +23,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "attention_sm100.h"
 #include "sm100_ptx.cuh"
 
@@ -44,6 +46,9 @@ constexpr int TILE_BYTES = BN * D * 2;       // 32 KB: one K or V tile, or one Q
 constexpr int HALF_BYTES = TILE_BYTES / 2;   // two 64-column halves, each 128 rows x 128 B
 constexpr int NSTAGE = 4;            // K/V ring depth (K_j and V_j take one stage each)
 constexpr float LAZY_TH = 8.0f;      // attention.metal:33-36
+// Largest a-priori logit bound (log2 units) for which it may stand in for the running max: every
+// p = exp2(x - bound) with x in [-bound, bound] then stays a normal fp32 / bf16 number (>= 2^-80).
+constexpr float kMaxStaticBound = 40.0f;
 
 // wait sites (reported in the status word)
 enum : uint32_t { SITE_Q = 1, SITE_KV_FULL = 2, SITE_KV_EMPTY = 3, SITE_S = 4, SITE_P = 5, SITE_PV = 6, SITE_DRAIN = 7 };
@@ -141,6 +146,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  KTRACE(threadIdx.x == 0, 30, 3);
 
   constexpr int WARP_TMA = NQ * 4, WARP_MMA = NQ * 4 + 1;
   if (warp < NQ * 4) {
@@ -157,202 +163,208 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (tile_active && n_tiles > 0) {
       // ---- stage Q (with the fused RMSNorm + RoPE prologue when weights are given) ----
-      // Pass 1 copies the raw row into its swizzled place (16-byte chunk c of row r goes to chunk slot
-      // c ^ (r & 7) of the row's 128 B line) while summing squares; pass 2 normalises and rotates in
-      // place, one chunk (pair of chunks for rotate-half) at a time so that few registers are live.
+      // Cooperative and coalesced: 16 lanes cover one row (one 16-byte chunk = 8 channels each), a warp
+      // takes two rows per step and 32 rows in all; sums of squares are reduced over the 16 lanes with
+      // shuffles.  16-byte chunk c of row r lands in chunk slot c ^ (r & 7) of the row's 128 B line
+      // (the 128-byte swizzle the MMA descriptors expect).
       {
-        const int rc = min(row, p.Lq - 1);               // rows past Lq are clamped, never stored
-        const uint4* src = (const uint4*)(p.Q + (size_t)b * p.bsq + (size_t)rc * p.ldq + (size_t)h * D);
-        uint8_t* qdst = q_smem + g * TILE_BYTES + r * 128;
-        auto slot = [&](int c) { return (uint4*)(qdst + (c >> 3) * HALF_BYTES + (((c & 7) ^ (r & 7)) << 4)); };
-        float ss = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < 16; c++) {
-          const uint4 v = __ldg(src + c);
-          *slot(c) = v;
-          const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float x0 = bf16lo_to_f32(w4[e]), x1 = bf16hi_to_f32(w4[e]);
-            ss = fmaf(x0, x0, ss);
-            ss = fmaf(x1, x1, ss);
-          }
+        const int sub = lane >> 4, c = lane & 15;
+        const bool norm = p.wq != nullptr;
+        float wv[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+        if (norm) {
+          const float4 wa = __ldg((const float4*)p.wq + 2 * c), wb = __ldg((const float4*)p.wq + 2 * c + 1);
+          wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
         }
-        if (p.wq != nullptr) {
-          const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
-          const int pos = p.q_row0 + rc;
-          const float4* cr = (const float4*)(p.cos + (size_t)pos * 64);
-          const float4* sr = (const float4*)(p.sin + (size_t)pos * 64);
-          const float4* wv = (const float4*)p.wq;
-          if (p.rope_mode == 1) {
-            // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), i.e. chunk c with chunk c + 8
-#pragma unroll 1
-            for (int c = 0; c < 8; c++) {
-              const uint4 lo = *slot(c), hi = *slot(c + 8);
-              const uint32_t lo4[4] = {lo.x, lo.y, lo.z, lo.w}, hi4[4] = {hi.x, hi.y, hi.z, hi.w};
-              uint32_t ol[4], oh[4];
+        const __nv_bfloat16* qhead = p.Q + (size_t)b * p.bsq + (size_t)h * D + 8 * c;
+#pragma unroll 4
+        for (int it = 0; it < 16; it++) {
+          const int rr = (warp & 3) * 32 + it * 2 + sub;            // row inside the tile
+          const int grow = min(q0 + g * BM + rr, p.Lq - 1);        // rows past Lq are clamped, never stored
+          uint4 v = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
+          if (norm) {
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+            float y[8];
+            float ss = 0.f;
 #pragma unroll
-              for (int hf = 0; hf < 2; hf++) {
-                const float4 wl = __ldg(wv + 2 * c + hf), wh = __ldg(wv + 16 + 2 * c + hf);
-                const float4 cc = __ldg(cr + 2 * c + hf), sc = __ldg(sr + 2 * c + hf);
-                const float wlf[4] = {wl.x, wl.y, wl.z, wl.w}, whf[4] = {wh.x, wh.y, wh.z, wh.w};
-                const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
-                float yl[4], yh[4];
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                  const uint32_t a = lo4[2 * hf + e], bb = hi4[2 * hf + e];
-                  const float xl0 = bf16lo_to_f32(a) * rrms * wlf[2 * e], xl1 = bf16hi_to_f32(a) * rrms * wlf[2 * e + 1];
-                  const float xh0 = bf16lo_to_f32(bb) * rrms * whf[2 * e], xh1 = bf16hi_to_f32(bb) * rrms * whf[2 * e + 1];
-                  yl[2 * e] = xl0 * cf[2 * e] - xh0 * sf[2 * e];
-                  yl[2 * e + 1] = xl1 * cf[2 * e + 1] - xh1 * sf[2 * e + 1];
-                  yh[2 * e] = xh0 * cf[2 * e] + xl0 * sf[2 * e];
-                  yh[2 * e + 1] = xh1 * cf[2 * e + 1] + xl1 * sf[2 * e + 1];
-                }
-                ol[2 * hf] = pack_bf16x2(yl[0], yl[1]);
-                ol[2 * hf + 1] = pack_bf16x2(yl[2], yl[3]);
-                oh[2 * hf] = pack_bf16x2(yh[0], yh[1]);
-                oh[2 * hf + 1] = pack_bf16x2(yh[2], yh[3]);
-              }
-              *slot(c) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
-              *slot(c + 8) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+            for (int e = 0; e < 4; e++) {
+              y[2 * e] = bf16lo_to_f32(w4[e]);
+              y[2 * e + 1] = bf16hi_to_f32(w4[e]);
+              ss = fmaf(y[2 * e], y[2 * e], ss);
+              ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
             }
-          } else {
-            const bool rot = p.rope_mode == 0;   // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113)
-#pragma unroll 1
-            for (int c = 0; c < 16; c++) {
-              const uint4 v = *slot(c);
-              const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-              const float4 wa = __ldg(wv + 2 * c), wb = __ldg(wv + 2 * c + 1);
-              const float ww[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-              float4 cc = make_float4(1.f, 1.f, 1.f, 1.f), sc = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (rot) {
-                cc = __ldg(cr + c);
-                sc = __ldg(sr + c);
-              }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
+#pragma unroll
+            for (int e = 0; e < 8; e++) y[e] *= rrms * wv[e];
+            const size_t trow = (size_t)(p.q_row0 + grow) * 64;
+            float z[8];
+            if (p.rope_mode == 0) {
+              // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113): this chunk holds pairs 4c..4c+3
+              const float4 cc = __ldg((const float4*)(p.cos + trow) + c), sc = __ldg((const float4*)(p.sin + trow) + c);
               const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
-              uint32_t o4[4];
 #pragma unroll
               for (int e = 0; e < 4; e++) {
-                const float x0 = bf16lo_to_f32(w4[e]) * rrms * ww[2 * e];
-                const float x1 = bf16hi_to_f32(w4[e]) * rrms * ww[2 * e + 1];
-                o4[e] = pack_bf16x2(x0 * cf[e] - x1 * sf[e], x0 * sf[e] + x1 * cf[e]);
+                z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
+                z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
               }
-              *slot(c) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+            } else if (p.rope_mode == 1) {
+              // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), held by the lane 8 chunks away
+              const int f = (c & 7) * 2;
+              const float4 c0 = __ldg((const float4*)(p.cos + trow) + f), c1 = __ldg((const float4*)(p.cos + trow) + f + 1);
+              const float4 s0 = __ldg((const float4*)(p.sin + trow) + f), s1 = __ldg((const float4*)(p.sin + trow) + f + 1);
+              const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+              const float sf[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+              const float sg = c < 8 ? -1.f : 1.f;
+#pragma unroll
+              for (int e = 0; e < 8; e++) {
+                const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
+                z[e] = y[e] * cf[e] + sg * other * sf[e];
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; e++) z[e] = y[e];
             }
+            v = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
           }
+          uint8_t* dst = q_smem + g * TILE_BYTES + rr * 128 + (c >> 3) * HALF_BYTES + (((c & 7) ^ (rr & 7)) << 4);
+          *(uint4*)dst = v;
         }
         fence_proxy_async_smem();
         mbar_arrive(&q_ready[g]);
       }
+      KTRACE(threadIdx.x == g * 128, 30 + g, 0);
 
-      // ---- online softmax over the key tiles ----
+      // ---- softmax over the key tiles ----
+      // Two forms of the same math.  Online: running row max, moved lazily (only when exceeded by more
+      // than 8 in log2 units, attention.metal:33-36), O rescaled when it moves.  Bounded: when the fused
+      // QK-RMSNorm prologue gives an a-priori bound on every logit (|q'| and |k'| are at most
+      // sqrt(128) * max|w|), that bound replaces the running max: softmax is invariant to the offset, so
+      // the result is the same, and the row-max pass, the vote and the rescale disappear.
       float m_i = -INFINITY;   // running max, log2 units (scaled scores)
-      float l_i = 0.f;         // running row sum of exp2(s - m_i), fp32
+      float l_i = 0.f;         // running row sum of exp2(s - m), fp32
       const float sc2 = p.scale_log2;
-      for (int j = 0; j < n_tiles; j++) {
-        const int kt = tile_of(j);
-        const int key0 = kt * BN;
-        KTRACE(threadIdx.x == g * 128, g * 8 + 0, j);
-        mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
-        tc_fence_after();
-        KTRACE(threadIdx.x == g * 128, g * 8 + 1, j);
-        uint32_t sv[128];
-        tmem_ld32(tS + 0, sv + 0);
-        tmem_ld32(tS + 32, sv + 32);
-        tmem_ld32(tS + 64, sv + 64);
-        tmem_ld32(tS + 96, sv + 96);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(s_free);     // the scores are in registers: the next Q K^T may overwrite the tile
-        KTRACE(threadIdx.x == g * 128, g * 8 + 2, j);
-        float* s = (float*)sv;
-        const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < 128; c++) {
-            const int key = key0 + c;
-            const bool ok = key < p.Lk && !(key >= pad_lo && key < pad_hi);
-            s[c] = ok ? s[c] : -INFINITY;
-          }
-        }
-        // row max: four independent chains of 3-input max
-        float mx4[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-        for (int c = 4; c < 128; c += 8) {
-#pragma unroll
-          for (int u = 0; u < 4; u++) mx4[u] = max3(mx4[u], s[c + 2 * u], s[c + 2 * u + 1]);
-        }
-        const float lm = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
-        const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
-        KTRACE(threadIdx.x == g * 128, g * 8 + 3, j);
-        bool rescale = false;                   // warp-uniform
-        float o_alpha = 1.f;
-        if (__any_sync(0xffffffffu, need)) {
-          const float m_new = need ? lm : m_i;
-          const float alpha = (m_i == -INFINITY) ? 0.f : ex2_approx(m_i - m_new);
-          m_i = m_new;
-          l_i *= alpha;
-          rescale = j > 0;
-          o_alpha = alpha;
-        }
-        const float m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
-        if (j > 0) {
-          // P V of the previous key tile still reads P_g (and, for a rescale, writes O_g) until this completes
-          mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+      const float bound = p.logit_bound != nullptr ? __ldg(p.logit_bound) : INFINITY;
+      auto softmax_tiles = [&](auto bounded_tag) {
+        constexpr bool BOUNDED = decltype(bounded_tag)::value;
+        for (int j = 0; j < n_tiles; j++) {
+          const int kt = tile_of(j);
+          const int key0 = kt * BN;
+          KTRACE(threadIdx.x == g * 128, g * 8 + 0, j);
+          mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
           tc_fence_after();
-        }
-        // p = exp2(s * scale_log2 - m): packed fp32x2 arithmetic; EMU of every 4 pairs take the
-        // polynomial exp2 on the FMA pipe instead of the (16/clk/SM) special-function unit
-        const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm2 = pack_f32x2(-m_use, -m_use);
-        uint64_t lsum2[2] = {0ull, 0ull};
+          KTRACE(threadIdx.x == g * 128, g * 8 + 1, j);
+          uint32_t sv[128];
+          tmem_ld32(tS + 0, sv + 0);
+          tmem_ld32(tS + 32, sv + 32);
+          tmem_ld32(tS + 64, sv + 64);
+          tmem_ld32(tS + 96, sv + 96);
+          tmem_wait_ld();
+          tc_fence_before();
+          mbar_arrive(s_free);     // the scores are in registers: the next Q K^T may overwrite the tile
+          KTRACE(threadIdx.x == g * 128, g * 8 + 2, j);
+          float* s = (float*)sv;
+          const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
+          if (need_mask) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; i++) {
-            const int c = ch * 32 + 2 * i;
-            const uint64_t x2 = fma_f32x2(pack_f32x2(s[c], s[c + 1]), sc2x2, negm2);
-            uint64_t p2;
-            if ((i & 3) < EMU) {
-              p2 = exp2_emulated_x2(x2);
-            } else {
-              float x0, x1;
-              unpack_f32x2(x2, x0, x1);
-              p2 = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+            for (int c = 0; c < 128; c++) {
+              const int key = key0 + c;
+              const bool ok = key < p.Lk && !(key >= pad_lo && key < pad_hi);
+              s[c] = ok ? s[c] : -INFINITY;
             }
-            lsum2[i & 1] = add_f32x2(lsum2[i & 1], p2);
-            float p0, p1;
-            unpack_f32x2(p2, p0, p1);
-            pk[i] = pack_bf16x2(p0, p1);
           }
-          tmem_st16(tP + ch * 16, pk);
-        }
-        {
-          float a0, a1, b0, b1;
-          unpack_f32x2(lsum2[0], a0, a1);
-          unpack_f32x2(lsum2[1], b0, b1);
-          l_i += (a0 + a1) + (b0 + b1);
-        }
-        KTRACE(threadIdx.x == g * 128, g * 8 + 4, j);
-        if (rescale) {
-          // the running max moved: rescale this row of O before P V of this tile may accumulate into it
-          // (P V of the previous tile has landed: see the wait above)
+          bool rescale = false;                   // warp-uniform
+          float o_alpha = 1.f;
+          float m_use;
+          if constexpr (BOUNDED) {
+            m_use = bound;
+          } else {
+            // row max: four independent chains of 3-input max
+            float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t ov[32];
-            tmem_ld32(tO + c0, ov);
-            tmem_wait_ld();
+            for (int c = 4; c < 128; c += 8) {
 #pragma unroll
-            for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * o_alpha);
-            tmem_st32(tO + c0, ov);
+              for (int u = 0; u < 4; u++) mx4[u] = max3(mx4[u], s[c + 2 * u], s[c + 2 * u + 1]);
+            }
+            const float lm = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
+            const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
+            if (__any_sync(0xffffffffu, need)) {
+              const float m_new = need ? lm : m_i;
+              const float alpha = (m_i == -INFINITY) ? 0.f : ex2_approx(m_i - m_new);
+              m_i = m_new;
+              l_i *= alpha;
+              rescale = j > 0;
+              o_alpha = alpha;
+            }
+            m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
           }
+          KTRACE(threadIdx.x == g * 128, g * 8 + 3, j);
+          if (j > 0) {
+            // P V of the previous key tile still reads P_g (and, for a rescale, writes O_g) until this completes
+            mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+            tc_fence_after();
+          }
+          // p = exp2(s * scale_log2 - m) in packed fp32x2 arithmetic, 32 keys at a time: all the scaling
+          // FMAs, then all the exponentials (EMU of every 4 pairs on the FMA pipe as a polynomial, the
+          // rest on the 16/clk/SM special-function unit), then the row sum and the bf16 packing.
+          const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm2 = pack_f32x2(-m_use, -m_use);
+          uint64_t lsum2[2] = {0ull, 0ull};
+#pragma unroll
+          for (int ch = 0; ch < 4; ch++) {
+            uint64_t x2[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) x2[i] = fma_f32x2(pack_f32x2(s[ch * 32 + 2 * i], s[ch * 32 + 2 * i + 1]), sc2x2, negm2);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              if ((i & 3) < EMU) {
+                x2[i] = exp2_emulated_x2(x2[i]);
+              } else {
+                float x0, x1;
+                unpack_f32x2(x2[i], x0, x1);
+                x2[i] = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) lsum2[i & 1] = add_f32x2(lsum2[i & 1], x2[i]);
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              float p0, p1;
+              unpack_f32x2(x2[i], p0, p1);
+              pk[i] = pack_bf16x2(p0, p1);
+            }
+            tmem_st16(tP + ch * 16, pk);
+          }
+          {
+            float a0, a1, b0, b1;
+            unpack_f32x2(lsum2[0], a0, a1);
+            unpack_f32x2(lsum2[1], b0, b1);
+            l_i += (a0 + a1) + (b0 + b1);
+          }
+          KTRACE(threadIdx.x == g * 128, g * 8 + 4, j);
+          if (rescale) {
+            // the running max moved: rescale this row of O before P V of this tile may accumulate into it
+            // (P V of the previous tile has landed: see the wait above)
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ov[32];
+              tmem_ld32(tO + c0, ov);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; c++) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * o_alpha);
+              tmem_st32(tO + c0, ov);
+            }
+          }
+          tmem_wait_st();
+          KTRACE(threadIdx.x == g * 128, g * 8 + 5, j);
+          tc_fence_before();
+          mbar_arrive(&p_full[g]);
         }
-        tmem_wait_st();
-        KTRACE(threadIdx.x == g * 128, g * 8 + 5, j);
-        tc_fence_before();
-        mbar_arrive(&p_full[g]);
-      }
+      };
+      if (bound <= kMaxStaticBound) softmax_tiles(std::true_type{});
+      else softmax_tiles(std::false_type{});
 
+      KTRACE(threadIdx.x == g * 128, 30 + g, 1);
       // ---- epilogue: O / l (x sigmoid(G)) -> bf16 ----
       mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV);
       tc_fence_after();
@@ -387,6 +399,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           }
         }
       }
+      KTRACE(threadIdx.x == g * 128, 30 + g, 2);
     } else if (tile_active && row < p.Lq) {
       // no visible key at all: zeros
       uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)row * p.ldo + (size_t)h * D);

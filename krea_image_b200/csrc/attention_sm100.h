@@ -24,6 +24,9 @@ struct AttnParams {
   float eps;
   int rope_mode;
   int q_row0;                  // sequence position of query row 0
+  // optional device float: an upper bound (log2 units, scale included) on every |logit|, written by the
+  // K pre-pass from the QK-norm weights; nullptr = unknown (plain operator on already-normalised input)
+  const float* logit_bound;
   // text key-padding: keys / query rows at positions [text_len[b], text_slots) are padding
   const int32_t* text_len;
   int text_slots;
@@ -54,6 +57,10 @@ struct NormRopeParams {
   int big_dim;
   float* qbig;
   float* kbig;
+  // joint call only: the pre-pass also derives the a-priori logit bound from both weight vectors
+  const float* bound_wq;       // nullptr = do not compute
+  float* bound_out;
+  float bound_scale_log2;      // softmax scale * log2(e)
 };
 cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream);
 

@@ -37,7 +37,8 @@ struct krea_cuda {
   uint64_t launches = 0;
   PFN_encodeTiled encode = nullptr;
   int nq = 2;                       // query tiles per CTA
-  int emu = 1;                      // of every 4 element pairs, how many take the polynomial exp2
+  int emu = 0;                      // of every 4 element pairs, how many take the polynomial exp2
+  bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
   bool profiling = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
   std::vector<cudaEvent_t> event_pool;
@@ -136,6 +137,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     const int v = atoi(s);
     if (v == 1 || v == 2) h->nq = v;
   }
+  if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);
     if (v >= 0 && v <= 3) h->emu = v;
@@ -290,6 +292,7 @@ struct AttnCall {
   int rope_mode, q_row0;
   const int32_t* text_len;
   int text_slots;
+  const float* logit_bound;
 };
 
 static int run_attention(krea_cuda* h, const AttnCall& c) {
@@ -321,6 +324,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);   // engine/src/metal.mm:198
   p.wq = c.wq; p.cos = c.cos; p.sin = c.sin; p.eps = c.eps; p.rope_mode = c.rope_mode; p.q_row0 = c.q_row0;
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
+  p.logit_bound = (h->static_bound && c.wq) ? c.logit_bound : nullptr;
   p.status = h->status_dev;
 
   CUtensorMap tmK, tmV;
@@ -390,6 +394,9 @@ static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* ks
   n.eps = a->eps;
   n.rope_mode = a->rope_mode;
   n.big_dim = -1;
+  n.bound_wq = a->wq;
+  n.bound_out = (float*)(h->status_dev + 8);   // a device float next to the status word
+  n.bound_scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);
   CUDA_TRY(h, cudaSetDevice(h->device));
   {
     ProfileMark pm(h, 0);
@@ -405,6 +412,7 @@ static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* ks
   c.bsq = a->bsq; c.bsk = n.bs_dst; c.bsv = a->bsv; c.bso = a->bso; c.bsg = c.G ? a->bsg : 0;
   c.wq = a->wq; c.cos = a->cos; c.sin = a->sin; c.eps = a->eps; c.rope_mode = a->rope_mode; c.q_row0 = a->q_row0;
   c.text_len = a->text_len; c.text_slots = a->text_slots;
+  c.logit_bound = n.bound_out;
   return run_attention(h, c);
 }
 

@@ -16,6 +16,20 @@ namespace krea {
 
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams p) {
   const int lane = threadIdx.x & 31;
+  if (p.bound_wq != nullptr && blockIdx.x == 0 && threadIdx.x < 32) {
+    // After RMSNorm every head vector has norm <= sqrt(128) * max|w| (RoPE is a rotation), so
+    // |q'.k'| <= 128 * max|wq| * max|wk|.  2% head-room covers the bf16 rounding of q' and k'
+    // (2^-8 each) and the approximate rsqrt.
+    const float4 a = __ldg((const float4*)p.bound_wq + lane), c = __ldg((const float4*)p.wk + lane);
+    float mq = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w)));
+    float mk = fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(c.z), fabsf(c.w)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mq = fmaxf(mq, __shfl_xor_sync(0xffffffffu, mq, o));
+      mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+    }
+    if (lane == 0) *p.bound_out = 128.0f * mq * mk * p.bound_scale_log2 * 1.02f;
+  }
   const int heads = p.n_q + p.n_k;
   const long long units = (long long)p.batch * p.rows * heads;
   const long long stride = (long long)gridDim.x * (blockDim.x >> 5);

@@ -169,67 +169,92 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // (the 128-byte swizzle the MMA descriptors expect).
       {
         const int sub = lane >> 4, c = lane & 15;
-        const bool norm = p.wq != nullptr;
-        float wv[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
-        if (norm) {
-          const float4 wa = __ldg((const float4*)p.wq + 2 * c), wb = __ldg((const float4*)p.wq + 2 * c + 1);
-          wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
-        }
         const __nv_bfloat16* qhead = p.Q + (size_t)b * p.bsq + (size_t)h * D + 8 * c;
-#pragma unroll 4
-        for (int it = 0; it < 16; it++) {
-          const int rr = (warp & 3) * 32 + it * 2 + sub;            // row inside the tile
-          const int grow = min(q0 + g * BM + rr, p.Lq - 1);        // rows past Lq are clamped, never stored
-          uint4 v = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
-          if (norm) {
-            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-            float y[8];
-            float ss = 0.f;
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              y[2 * e] = bf16lo_to_f32(w4[e]);
-              y[2 * e + 1] = bf16hi_to_f32(w4[e]);
-              ss = fmaf(y[2 * e], y[2 * e], ss);
-              ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
-            }
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
-#pragma unroll
-            for (int e = 0; e < 8; e++) y[e] *= rrms * wv[e];
-            const size_t trow = (size_t)(p.q_row0 + grow) * 64;
-            float z[8];
-            if (p.rope_mode == 0) {
-              // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113): this chunk holds pairs 4c..4c+3
-              const float4 cc = __ldg((const float4*)(p.cos + trow) + c), sc = __ldg((const float4*)(p.sin + trow) + c);
-              const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
-#pragma unroll
-              for (int e = 0; e < 4; e++) {
-                z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
-                z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
-              }
-            } else if (p.rope_mode == 1) {
-              // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), held by the lane 8 chunks away
-              const int f = (c & 7) * 2;
-              const float4 c0 = __ldg((const float4*)(p.cos + trow) + f), c1 = __ldg((const float4*)(p.cos + trow) + f + 1);
-              const float4 s0 = __ldg((const float4*)(p.sin + trow) + f), s1 = __ldg((const float4*)(p.sin + trow) + f + 1);
-              const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-              const float sf[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-              const float sg = c < 8 ? -1.f : 1.f;
-#pragma unroll
-              for (int e = 0; e < 8; e++) {
-                const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
-                z[e] = y[e] * cf[e] + sg * other * sf[e];
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; e++) z[e] = y[e];
-            }
-            v = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
+        // MODE 0 / 1 / 2: RMSNorm + interleaved-pair / rotate-half / no RoPE; MODE 3: copy as it is.
+        // Eight rows per lane are in flight at a time: all their global loads are issued before any of
+        // them is used, so the staging costs about two memory round trips instead of sixteen.
+        auto stage_q = [&](auto mode_tag) {
+          constexpr int MODE = decltype(mode_tag)::value;
+          float wv[8];
+          if constexpr (MODE != 3) {
+            const float4 wa = __ldg((const float4*)p.wq + 2 * c), wb = __ldg((const float4*)p.wq + 2 * c + 1);
+            wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
           }
-          uint8_t* dst = q_smem + g * TILE_BYTES + rr * 128 + (c >> 3) * HALF_BYTES + (((c & 7) ^ (rr & 7)) << 4);
-          *(uint4*)dst = v;
-        }
+#pragma unroll 1
+          for (int half = 0; half < 2; half++) {
+            uint4 raw[8];
+            float4 t0[8], t1[8];     // MODE 0: cos, sin of this chunk's 4 pairs; MODE 1: cos (2 x float4 in t0/t1)
+            float4 t2[8], t3[8];     // MODE 1: sin
+            int rr[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              rr[i] = (warp & 3) * 32 + (half * 8 + i) * 2 + sub;       // row inside the tile
+              const int grow = min(q0 + g * BM + rr[i], p.Lq - 1);     // rows past Lq are clamped, never stored
+              raw[i] = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
+              const size_t trow = (size_t)(p.q_row0 + grow) * 64;
+              if constexpr (MODE == 0) {
+                t0[i] = __ldg((const float4*)(p.cos + trow) + c);
+                t1[i] = __ldg((const float4*)(p.sin + trow) + c);
+              } else if constexpr (MODE == 1) {
+                const int f = (c & 7) * 2;
+                t0[i] = __ldg((const float4*)(p.cos + trow) + f);
+                t1[i] = __ldg((const float4*)(p.cos + trow) + f + 1);
+                t2[i] = __ldg((const float4*)(p.sin + trow) + f);
+                t3[i] = __ldg((const float4*)(p.sin + trow) + f + 1);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              uint4 v = raw[i];
+              if constexpr (MODE != 3) {
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+                float y[8], z[8];
+                float ss = 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  y[2 * e] = bf16lo_to_f32(w4[e]);
+                  y[2 * e + 1] = bf16hi_to_f32(w4[e]);
+                  ss = fmaf(y[2 * e], y[2 * e], ss);
+                  ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
+                }
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float rrms = rsqrtf(ss * (1.0f / D) + p.eps);
+#pragma unroll
+                for (int e = 0; e < 8; e++) y[e] *= rrms * wv[e];
+                if constexpr (MODE == 0) {
+                  // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113): this chunk holds pairs 4c..4c+3
+                  const float cf[4] = {t0[i].x, t0[i].y, t0[i].z, t0[i].w}, sf[4] = {t1[i].x, t1[i].y, t1[i].z, t1[i].w};
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
+                    z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
+                  }
+                } else if constexpr (MODE == 1) {
+                  // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), held by the lane 8 chunks away
+                  const float cf[8] = {t0[i].x, t0[i].y, t0[i].z, t0[i].w, t1[i].x, t1[i].y, t1[i].z, t1[i].w};
+                  const float sf[8] = {t2[i].x, t2[i].y, t2[i].z, t2[i].w, t3[i].x, t3[i].y, t3[i].z, t3[i].w};
+                  const float sg = c < 8 ? -1.f : 1.f;
+#pragma unroll
+                  for (int e = 0; e < 8; e++) {
+                    const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
+                    z[e] = y[e] * cf[e] + sg * other * sf[e];
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; e++) z[e] = y[e];
+                }
+                v = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
+              }
+              uint8_t* dst = q_smem + g * TILE_BYTES + rr[i] * 128 + (c >> 3) * HALF_BYTES + (((c & 7) ^ (rr[i] & 7)) << 4);
+              *(uint4*)dst = v;
+            }
+          }
+        };
+        if (p.wq == nullptr) stage_q(std::integral_constant<int, 3>{});
+        else if (p.rope_mode == 0) stage_q(std::integral_constant<int, 0>{});
+        else if (p.rope_mode == 1) stage_q(std::integral_constant<int, 1>{});
+        else stage_q(std::integral_constant<int, 2>{});
         fence_proxy_async_smem();
         mbar_arrive(&q_ready[g]);
       }

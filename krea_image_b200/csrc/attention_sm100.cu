@@ -390,38 +390,57 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       else softmax_tiles(std::false_type{});
 
       KTRACE(threadIdx.x == g * 128, 30 + g, 1);
-      // ---- epilogue: O / l (x sigmoid(G)) -> bf16 ----
+      // ---- epilogue: O / l (x sigmoid(G)) -> bf16, staged through shared memory for coalesced stores ----
+      // Each thread owns one row in TMEM, but a row is 256 contiguous bytes in global memory: the tile is
+      // first written to the (now idle) Q buffer of this tile, 16-byte chunk c of row r in chunk slot
+      // c ^ (r & 15), and then stored with 16 lanes per row so that every store instruction of a warp
+      // writes two full 256-byte rows.
       mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV);
       tc_fence_after();
+      KTRACE(threadIdx.x == g * 128, 30 + g, 4);
       const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
       const int pos = p.q_row0 + row;
       const bool padded_row = pos >= pad_lo && pos < pad_hi;
-      const bool store_row = row < p.Lq;
-      const int rs = store_row ? row : 0;
-      uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)rs * p.ldo + (size_t)h * D);
+      const int rs = min(row, p.Lq - 1);
       const uint4* gsrc = p.G ? (const uint4*)(p.G + (size_t)b * p.bsg + (size_t)rs * p.ldg + (size_t)h * D) : nullptr;
-#pragma unroll
+      uint8_t* ostage = q_smem + g * TILE_BYTES;
+#pragma unroll 1   // executed once per CTA: compact code beats unrolled code that has to be fetched cold
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t ov[32];
-        tmem_ld32(tO + c0, ov);   // .sync.aligned: executed by the whole warp, stores are predicated below
+        tmem_ld32(tO + c0, ov);
         tmem_wait_ld();
-        if (store_row) {
+        KTRACE(threadIdx.x == g * 128, 32 + g, 2 * (c0 >> 5));
 #pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) {
-            float f[8];
+        for (int q4 = 0; q4 < 4; q4++) {
+          float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; e++) f[e] = padded_row ? 0.f : __uint_as_float(ov[q4 * 8 + e]) * inv;
-            if (gsrc) {
-              const uint4 gv = __ldg(gsrc + (c0 >> 3) + q4);
-              const uint32_t g4[4] = {gv.x, gv.y, gv.z, gv.w};
+          for (int e = 0; e < 8; e++) f[e] = padded_row ? 0.f : __uint_as_float(ov[q4 * 8 + e]) * inv;
+          if (gsrc) {
+            const uint4 gv = __ldg(gsrc + (c0 >> 3) + q4);
+            const uint32_t g4[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-              for (int e = 0; e < 4; e++) {
-                f[2 * e] *= 1.0f / (1.0f + __expf(-bf16lo_to_f32(g4[e])));
-                f[2 * e + 1] *= 1.0f / (1.0f + __expf(-bf16hi_to_f32(g4[e])));
-              }
+            for (int e = 0; e < 4; e++) {
+              f[2 * e] *= 1.0f / (1.0f + __expf(-bf16lo_to_f32(g4[e])));        // common.h:24 sigmoid
+              f[2 * e + 1] *= 1.0f / (1.0f + __expf(-bf16hi_to_f32(g4[e])));
             }
-            dst[(c0 >> 3) + q4] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
           }
+          const int ch = (c0 >> 3) + q4;
+          *(uint4*)(ostage + r * 256 + ((ch ^ (r & 15)) << 4)) =
+              make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        }
+        KTRACE(threadIdx.x == g * 128, 32 + g, 2 * (c0 >> 5) + 1);
+      }
+      KTRACE(threadIdx.x == g * 128, 30 + g, 5);
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");   // the 128 threads of this warpgroup
+      {
+        const int sub = lane >> 4, ch = lane & 15;
+        __nv_bfloat16* obase = p.O + (size_t)b * p.bso + (size_t)h * D + 8 * ch;
+#pragma unroll 4
+        for (int it = 0; it < 16; it++) {
+          const int rr = (warp & 3) * 32 + it * 2 + sub;
+          const int grow = q0 + g * BM + rr;
+          const uint4 v = *(const uint4*)(ostage + rr * 256 + ((ch ^ (rr & 15)) << 4));
+          if (grow < p.Lq) *(uint4*)(obase + (size_t)grow * p.ldo) = v;
         }
       }
       KTRACE(threadIdx.x == g * 128, 30 + g, 2);

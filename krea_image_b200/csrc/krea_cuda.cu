@@ -230,10 +230,12 @@ int krea_cuda_qk_norm_rope(krea_cuda* h, const krea_cuda_qknorm_args* a) {
   if (!a->qkv || (a->n_q > 0 && !a->wq) || (a->n_k > 0 && !a->wk)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: null tensor");
   if (a->rope_mode < 0 || a->rope_mode > 2) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: rope_mode must be 0, 1 or 2");
   if (a->rope_mode != KREA_CUDA_ROPE_NONE && (!a->cos || !a->sin)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: cos/sin tables missing");
-  if (a->ld % 4 || a->q_off % 4 || a->k_off % 4 || ((uintptr_t)a->qkv & 7u))
-    return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: ld, q_off, k_off must be multiples of 4 and qkv 8-byte aligned");
+  if (a->ld % 8 || a->q_off % 8 || a->k_off % 8 || !aligned16(a->qkv))
+    return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: ld, q_off, k_off must be multiples of 8 and qkv 16-byte aligned");
   if (a->q_off < 0 || a->k_off < 0 || (a->n_q > 0 && a->q_off + a->n_q * 128 > a->ld) || (a->n_k > 0 && a->k_off + a->n_k * 128 > a->ld))
     return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: heads do not fit in a row of ld elements");
+  if (!aligned16(a->wq) || !aligned16(a->wk) || !aligned16(a->cos) || !aligned16(a->sin))
+    return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: weights and tables must be 16-byte aligned");
   if (a->big_dim >= 128) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: big_dim out of range");
   // the reference throws here too (engine/src/metal.mm:185)
   if (a->big_dim >= 0 && (!a->qbig || !a->kbig)) return fail(h, KREA_CUDA_E_ARG, "qk_norm_rope: big_dim needs qbig / kbig");
@@ -424,6 +426,8 @@ static int validate_joint(krea_cuda* h, const krea_cuda_joint_args* a) {
   if (a->rope_mode < 0 || a->rope_mode > 2) return fail(h, KREA_CUDA_E_ARG, "joint_attention: rope_mode must be 0, 1 or 2");
   if (a->rope_mode != KREA_CUDA_ROPE_NONE && (!a->cos || !a->sin)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: cos/sin tables missing");
   if (a->Lk > 0 && (!a->K || !a->V)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: null tensor");
+  if (!aligned16(a->wq) || !aligned16(a->wk) || !aligned16(a->cos) || !aligned16(a->sin))
+    return fail(h, KREA_CUDA_E_ARG, "joint_attention: weights and tables must be 16-byte aligned");
   if (a->ldk % 8 || a->bsk % 8 || !aligned16(a->K)) return fail(h, KREA_CUDA_E_ARG, "joint_attention: K must be 16-byte aligned with ld, batch stride multiples of 8");
   if (a->ldk < (int64_t)(a->heads / a->group) * 128) return fail(h, KREA_CUDA_E_ARG, "joint_attention: ldk smaller than kv heads*128");
   return KREA_CUDA_OK;

@@ -2,9 +2,8 @@
 // Metal::qk_norm_rope of the reference (engine/kernels/norm.metal:81-134), plus an out-of-place form
 // with batch strides used as the K pre-pass of the fused joint-attention call.
 //
-// HBM-bound elementwise pass: one warp per (row, head), each lane owns 4 consecutive channels (one
-// 8-byte load and one 8-byte store per lane, 256 contiguous bytes per warp); sums of squares are
-// reduced with shuffles; all math in fp32; the result is rounded to bf16 once, at the store.
+// HBM-bound elementwise pass; sums of squares are reduced with shuffles; all math in fp32; the result is
+// rounded to bf16 once, at the store.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -14,6 +13,10 @@
 
 namespace krea {
 
+// One warp per row (grid-stride over batch x rows), looping over the row's heads two at a time: 16 lanes
+// cover one head with 16 bytes (8 channels) each, so a warp load is 512 contiguous bytes.  The row's
+// cos/sin entries and the weights depend only on the lane's channels, not on the head, and stay in
+// registers across the head loop.
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams p) {
   const int lane = threadIdx.x & 31;
   if (p.bound_wq != nullptr && blockIdx.x == 0 && threadIdx.x < 32) {
@@ -30,65 +33,104 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
     }
     if (lane == 0) *p.bound_out = 128.0f * mq * mk * p.bound_scale_log2 * 1.02f;
   }
+  const int sub = lane >> 4, c = lane & 15;     // which of the two heads of a step, which 8-channel chunk
   const int heads = p.n_q + p.n_k;
-  const long long units = (long long)p.batch * p.rows * heads;
-  const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < units; unit += stride) {
-    const int hh = (int)(unit % heads);
-    const long long rb = unit / heads;
-    const int row = (int)(rb % p.rows);
-    const int b = (int)(rb / p.rows);
-    const bool is_q = hh < p.n_q;
-    const int hl = is_q ? hh : hh - p.n_q;
-    const size_t src_col = (size_t)(is_q ? p.q_off : p.k_off) + (size_t)hl * 128;
-    const size_t dst_col = (size_t)(is_q ? p.q_off_dst : p.k_off_dst) + (size_t)hl * 128;
-    const uint2 raw = __ldg((const uint2*)(p.src + (size_t)b * p.bs_src + (size_t)row * p.ld_src + src_col) + lane);
-    float x0 = bf16lo_to_f32(raw.x), x1 = bf16hi_to_f32(raw.x), x2 = bf16lo_to_f32(raw.y), x3 = bf16hi_to_f32(raw.y);
-    float ss = x0 * x0 + x1 * x1 + x2 * x2 + x3 * x3;
+  float wqv[8], wkv[8];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
-    const float4 w = __ldg((const float4*)(is_q ? p.wq : p.wk) + lane);
-    x0 *= rrms * w.x; x1 *= rrms * w.y; x2 *= rrms * w.z; x3 *= rrms * w.w;
-    float o0 = x0, o1 = x1, o2 = x2, o3 = x3;
+  for (int e = 0; e < 8; e++) wqv[e] = wkv[e] = 0.f;
+  if (p.n_q > 0) {
+    const float4 a = __ldg((const float4*)p.wq + 2 * c), bq = __ldg((const float4*)p.wq + 2 * c + 1);
+    wqv[0] = a.x; wqv[1] = a.y; wqv[2] = a.z; wqv[3] = a.w; wqv[4] = bq.x; wqv[5] = bq.y; wqv[6] = bq.z; wqv[7] = bq.w;
+  }
+  if (p.n_k > 0) {
+    const float4 a = __ldg((const float4*)p.wk + 2 * c), bk = __ldg((const float4*)p.wk + 2 * c + 1);
+    wkv[0] = a.x; wkv[1] = a.y; wkv[2] = a.z; wkv[3] = a.w; wkv[4] = bk.x; wkv[5] = bk.y; wkv[6] = bk.z; wkv[7] = bk.w;
+  }
+  const int nrows = p.batch * p.rows;
+  const int wstride = gridDim.x * (blockDim.x >> 5);
+  for (int rb = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); rb < nrows; rb += wstride) {
+    const int b = rb / p.rows, row = rb - b * p.rows;
+    const __nv_bfloat16* srow = p.src + (size_t)b * p.bs_src + (size_t)row * p.ld_src;
+    __nv_bfloat16* drow = p.dst + (size_t)b * p.bs_dst + (size_t)row * p.ld_dst;
     const size_t trow = (size_t)(p.row0 + row) * 64;
+    float cf[8], sf[8];
     if (p.rope_mode == 0) {
-      // interleaved pairs (2i, 2i+1) share frequency i: this lane holds pairs 2*lane and 2*lane+1
-      const float2 c = __ldg((const float2*)(p.cos + trow) + lane), s = __ldg((const float2*)(p.sin + trow) + lane);
-      o0 = x0 * c.x - x1 * s.x;
-      o1 = x0 * s.x + x1 * c.x;
-      o2 = x2 * c.y - x3 * s.y;
-      o3 = x2 * s.y + x3 * c.y;
+      // interleaved pairs (2i, 2i+1) share frequency i: this chunk holds pairs 4c .. 4c+3
+      const float4 cc = __ldg((const float4*)(p.cos + trow) + c), sc = __ldg((const float4*)(p.sin + trow) + c);
+      cf[0] = cc.x; cf[1] = cc.y; cf[2] = cc.z; cf[3] = cc.w;
+      sf[0] = sc.x; sf[1] = sc.y; sf[2] = sc.z; sf[3] = sc.w;
     } else if (p.rope_mode == 1) {
-      // rotate-half: channel i pairs with i + 64, whose owner is lane ^ 16
-      const float y0 = __shfl_xor_sync(0xffffffffu, x0, 16), y1 = __shfl_xor_sync(0xffffffffu, x1, 16);
-      const float y2 = __shfl_xor_sync(0xffffffffu, x2, 16), y3 = __shfl_xor_sync(0xffffffffu, x3, 16);
-      const float4 c = __ldg((const float4*)(p.cos + trow) + (lane & 15)), s = __ldg((const float4*)(p.sin + trow) + (lane & 15));
-      const float sg = lane < 16 ? -1.f : 1.f;
-      o0 = x0 * c.x + sg * y0 * s.x;
-      o1 = x1 * c.y + sg * y1 * s.y;
-      o2 = x2 * c.z + sg * y2 * s.z;
-      o3 = x3 * c.w + sg * y3 * s.w;
+      // rotate-half: channel i pairs with i + 64 (the lane 8 chunks away); both use frequency i mod 64
+      const int f = (c & 7) * 2;
+      const float4 c0 = __ldg((const float4*)(p.cos + trow) + f), c1 = __ldg((const float4*)(p.cos + trow) + f + 1);
+      const float4 s0 = __ldg((const float4*)(p.sin + trow) + f), s1 = __ldg((const float4*)(p.sin + trow) + f + 1);
+      cf[0] = c0.x; cf[1] = c0.y; cf[2] = c0.z; cf[3] = c0.w; cf[4] = c1.x; cf[5] = c1.y; cf[6] = c1.z; cf[7] = c1.w;
+      sf[0] = s0.x; sf[1] = s0.y; sf[2] = s0.z; sf[3] = s0.w; sf[4] = s1.x; sf[5] = s1.y; sf[6] = s1.z; sf[7] = s1.w;
     }
-    if (p.big_dim >= 0 && lane == (p.big_dim >> 2)) {
-      const int e = p.big_dim & 3;
-      const float v = e == 0 ? o0 : e == 1 ? o1 : e == 2 ? o2 : o3;
-      if (is_q) p.qbig[((size_t)b * p.rows + row) * p.n_q + hl] = v;
-      else p.kbig[((size_t)b * p.rows + row) * p.n_k + hl] = v;
-      if (e == 0) o0 = 0.f; else if (e == 1) o1 = 0.f; else if (e == 2) o2 = 0.f; else o3 = 0.f;
+#pragma unroll 2
+    for (int h0 = 0; h0 < heads; h0 += 2) {
+      const int hh = h0 + sub;
+      const bool live = hh < heads;               // odd head count: the upper half-warp idles on the last step
+      const int hc = live ? hh : heads - 1;
+      const bool is_q = hc < p.n_q;
+      const int hl = is_q ? hc : hc - p.n_q;
+      const int scol = (is_q ? p.q_off : p.k_off) + hl * 128 + 8 * c;
+      const int dcol = (is_q ? p.q_off_dst : p.k_off_dst) + hl * 128 + 8 * c;
+      const uint4 raw = __ldg((const uint4*)(srow + scol));
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+      float y[8], z[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        y[2 * e] = bf16lo_to_f32(w4[e]);
+        y[2 * e + 1] = bf16hi_to_f32(w4[e]);
+        ss = fmaf(y[2 * e], y[2 * e], ss);
+        ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+#pragma unroll
+      for (int e = 0; e < 8; e++) y[e] *= rrms * (is_q ? wqv[e] : wkv[e]);
+      if (p.rope_mode == 0) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
+          z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
+        }
+      } else if (p.rope_mode == 1) {
+        const float sg = c < 8 ? -1.f : 1.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
+          z[e] = y[e] * cf[e] + sg * other * sf[e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e++) z[e] = y[e];
+      }
+      if (p.big_dim >= 0 && c == (p.big_dim >> 3)) {
+        // that channel goes to the fp32 side buffer and is stored as zero (norm.metal:127-132)
+        const int e = p.big_dim & 7;
+        float v = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+          if (i == e) { v = z[i]; z[i] = 0.f; }
+        if (live) {
+          if (is_q) p.qbig[((size_t)b * p.rows + row) * p.n_q + hl] = v;
+          else p.kbig[((size_t)b * p.rows + row) * p.n_k + hl] = v;
+        }
+      }
+      if (live) *(uint4*)(drow + dcol) = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
     }
-    uint2 out;
-    out.x = pack_bf16x2(o0, o1);
-    out.y = pack_bf16x2(o2, o3);
-    *((uint2*)(p.dst + (size_t)b * p.bs_dst + (size_t)row * p.ld_dst + dst_col) + lane) = out;
   }
 }
 
 cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
-  const long long units = (long long)p.batch * p.rows * (p.n_q + p.n_k);
-  if (units <= 0) return cudaSuccess;
-  long long blocks = (units + 7) / 8;
-  const long long cap = 148LL * 8 * 4;   // a few waves of 8 resident CTAs per SM; the loop strides over the rest
+  const long long nrows = (long long)p.batch * p.rows;
+  if (nrows <= 0 || p.n_q + p.n_k <= 0) return cudaSuccess;
+  long long blocks = (nrows + 7) / 8;    // 8 warps per CTA, one row per warp and step
+  const long long cap = 148LL * 8;       // all resident at once; the loop strides over the rest
   if (blocks > cap) blocks = cap;
   qk_norm_rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
   return cudaGetLastError();

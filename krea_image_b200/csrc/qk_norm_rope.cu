@@ -67,61 +67,71 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
       cf[0] = c0.x; cf[1] = c0.y; cf[2] = c0.z; cf[3] = c0.w; cf[4] = c1.x; cf[5] = c1.y; cf[6] = c1.z; cf[7] = c1.w;
       sf[0] = s0.x; sf[1] = s0.y; sf[2] = s0.z; sf[3] = s0.w; sf[4] = s1.x; sf[5] = s1.y; sf[6] = s1.z; sf[7] = s1.w;
     }
-#pragma unroll 2
-    for (int h0 = 0; h0 < heads; h0 += 2) {
-      const int hh = h0 + sub;
-      const bool live = hh < heads;               // odd head count: the upper half-warp idles on the last step
-      const int hc = live ? hh : heads - 1;
-      const bool is_q = hc < p.n_q;
-      const int hl = is_q ? hc : hc - p.n_q;
-      const int scol = (is_q ? p.q_off : p.k_off) + hl * 128 + 8 * c;
-      const int dcol = (is_q ? p.q_off_dst : p.k_off_dst) + hl * 128 + 8 * c;
-      const uint4 raw = __ldg((const uint4*)(srow + scol));
-      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
-      float y[8], z[8];
-      float ss = 0.f;
+    // four steps (eight heads) per batch: their loads are all issued before the first one is used
+    for (int hb = 0; hb < heads; hb += 8) {
+      uint4 raw[4];
+      int dcol[4], hl[4];
+      bool live[4], isq[4];
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        y[2 * e] = bf16lo_to_f32(w4[e]);
-        y[2 * e + 1] = bf16hi_to_f32(w4[e]);
-        ss = fmaf(y[2 * e], y[2 * e], ss);
-        ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
+      for (int i = 0; i < 4; i++) {
+        const int hh = hb + 2 * i + sub;
+        live[i] = hh < heads;                      // ragged head count: idle lanes re-read the last head
+        const int hc = live[i] ? hh : heads - 1;
+        isq[i] = hc < p.n_q;
+        hl[i] = isq[i] ? hc : hc - p.n_q;
+        const int scol = (isq[i] ? p.q_off : p.k_off) + hl[i] * 128 + 8 * c;
+        dcol[i] = (isq[i] ? p.q_off_dst : p.k_off_dst) + hl[i] * 128 + 8 * c;
+        raw[i] = __ldg((const uint4*)(srow + scol));
       }
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
-#pragma unroll
-      for (int e = 0; e < 8; e++) y[e] *= rrms * (is_q ? wqv[e] : wkv[e]);
-      if (p.rope_mode == 0) {
+      for (int i = 0; i < 4; i++) {
+        if (hb + 2 * i >= heads) break;            // warp-uniform
+        const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+        float y[8], z[8];
+        float ss = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-          z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
-          z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
+          y[2 * e] = bf16lo_to_f32(w4[e]);
+          y[2 * e + 1] = bf16hi_to_f32(w4[e]);
+          ss = fmaf(y[2 * e], y[2 * e], ss);
+          ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
         }
-      } else if (p.rope_mode == 1) {
-        const float sg = c < 8 ? -1.f : 1.f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-          const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
-          z[e] = y[e] * cf[e] + sg * other * sf[e];
+        for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+#pragma unroll
+        for (int e = 0; e < 8; e++) y[e] *= rrms * (isq[i] ? wqv[e] : wkv[e]);
+        if (p.rope_mode == 0) {
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
+            z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
+          }
+        } else if (p.rope_mode == 1) {
+          const float sg = c < 8 ? -1.f : 1.f;
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const float other = __shfl_xor_sync(0xffffffffu, y[e], 8);
+            z[e] = y[e] * cf[e] + sg * other * sf[e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; e++) z[e] = y[e];
         }
-      } else {
+        if (p.big_dim >= 0 && c == (p.big_dim >> 3)) {
+          // that channel goes to the fp32 side buffer and is stored as zero (norm.metal:127-132)
+          const int e = p.big_dim & 7;
+          float v = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) z[e] = y[e];
+          for (int k = 0; k < 8; k++)
+            if (k == e) { v = z[k]; z[k] = 0.f; }
+          if (live[i]) {
+            if (isq[i]) p.qbig[((size_t)b * p.rows + row) * p.n_q + hl[i]] = v;
+            else p.kbig[((size_t)b * p.rows + row) * p.n_k + hl[i]] = v;
+          }
+        }
+        if (live[i]) *(uint4*)(drow + dcol[i]) = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
       }
-      if (p.big_dim >= 0 && c == (p.big_dim >> 3)) {
-        // that channel goes to the fp32 side buffer and is stored as zero (norm.metal:127-132)
-        const int e = p.big_dim & 7;
-        float v = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-          if (i == e) { v = z[i]; z[i] = 0.f; }
-        if (live) {
-          if (is_q) p.qbig[((size_t)b * p.rows + row) * p.n_q + hl] = v;
-          else p.kbig[((size_t)b * p.rows + row) * p.n_k + hl] = v;
-        }
-      }
-      if (live) *(uint4*)(drow + dcol) = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
     }
   }
 }

@@ -160,6 +160,27 @@ typedef struct {
 KREA_CUDA_API size_t krea_cuda_joint_scratch_bytes(const krea_cuda_joint_args* a);
 KREA_CUDA_API int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_args* a);
 
+/* The fused call for callers that cannot allocate device memory.  No counterpart in the reference (its
+ * operators never allocate either, but they also need no scratch: the reference normalises K in place).
+ * Who needs it: code that runs after all device memory has been handed to another owner (a framework's
+ * caching allocator, a fixed-partition inference server), code on a latency-critical path where
+ * cudaMalloc's implicit device-wide synchronisation is not acceptable, and hosts whose rules forbid
+ * allocation after start-up.  Those callers cannot give krea_cuda_joint_attention a k_scratch of their own
+ * and must not let the handle grow one.
+ * Same arguments and results as krea_cuda_joint_attention (k_scratch / k_scratch_bytes are ignored), but the
+ * normalised K goes to a fixed KREA_CUDA_STATIC_SCRATCH_BYTES array that is part of the library's device
+ * image: every GPU on which the library is used keeps those 32 MiB reserved until the process exits.
+ *  - Limit: batch * Lk * (heads/group) * 256 bytes must fit in the array (e.g. one sample of 24 heads x
+ *    5461 keys); larger problems return KREA_CUDA_E_NOMEM with a message and launch nothing.
+ *  - The call itself performs no cudaMalloc / cudaFree and calls no allocating library routine.  The first
+ *    call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *    before any stream capture begins.
+ *  - All calls, from every handle on the same device, share the one array: it keeps the previous call's
+ *    contents (nothing needs clearing - each call overwrites what it reads), and two calls whose kernels
+ *    can overlap on the GPU (different streams without ordering) race on it.  Serialise them. */
+#define KREA_CUDA_STATIC_SCRATCH_BYTES (32u << 20)
+KREA_CUDA_API int krea_cuda_joint_attention_static(krea_cuda* h, const krea_cuda_joint_args* a);
+
 /* Same call with every pointer in HOST memory (the reference's Tensor is CPU-visible unified memory,
  * engine/src/metal.h:14-23): copies the operands to device buffers owned by the handle, runs
  * krea_cuda_joint_attention, copies O back and synchronises.  Pinned host memory makes the copies

@@ -11,6 +11,7 @@ from . import build as _build
 
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM = 0, -1, -2, -3, -4, -5
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
+STATIC_SCRATCH_BYTES = 32 << 20   # KREA_CUDA_STATIC_SCRATCH_BYTES
 
 _vp = ctypes.c_void_p
 _int = ctypes.c_int
@@ -63,6 +64,7 @@ SYMBOLS = {
     "krea_cuda_joint_scratch_bytes": (ctypes.c_size_t, [ctypes.POINTER(JointArgs)]),
     "krea_cuda_joint_attention": (_int, [_vp, ctypes.POINTER(JointArgs)]),
     "krea_cuda_joint_attention_host": (_int, [_vp, ctypes.POINTER(JointArgs)]),
+    "krea_cuda_joint_attention_static": (_int, [_vp, ctypes.POINTER(JointArgs)]),
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
     "krea_cuda_reshard_pack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),

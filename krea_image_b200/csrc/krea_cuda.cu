@@ -10,6 +10,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <string>
 #include <utility>
 #include <vector>
@@ -466,6 +467,53 @@ int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_args* a) {
     return run_attention(h, c);
   }
   return joint_on_device(h, a, kscr);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The fused call for callers that must not allocate device memory.  Its scratch (the normalised and
+// rotated K that the pre-pass hands to the attention kernel) lives in a fixed array in the library's
+// device image instead of memory obtained at run time.  In host code the array's name is only a
+// stand-in for the device symbol - it is not a device address - so the address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and that pointer is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_k_scratch[KREA_CUDA_STATIC_SCRATCH_BYTES];
+static void* g_static_k_scratch_ptr[64] = {};
+static std::mutex g_static_k_scratch_mutex;
+
+int krea_cuda_joint_attention_static(krea_cuda* h, const krea_cuda_joint_args* a) {
+  int rc = validate_joint(h, a);
+  if (rc) return rc;
+  if (a->Lq == 0 || a->heads == 0) return KREA_CUDA_OK;
+  const size_t need = krea_cuda_joint_scratch_bytes(a);
+  if (need > (size_t)KREA_CUDA_STATIC_SCRATCH_BYTES)
+    return fail(h, KREA_CUDA_E_NOMEM,
+                "joint_attention_static: batch * Lk * kv_heads * 256 = %zu bytes of normalised K exceed the built-in %zu-byte "
+                "scratch; use krea_cuda_joint_attention with caller-provided k_scratch for this size",
+                need, (size_t)KREA_CUDA_STATIC_SCRATCH_BYTES);
+  if (h->device < 0 || h->device >= 64) return fail(h, KREA_CUDA_E_ARG, "joint_attention_static: device index above 63");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_k_scratch_mutex);
+    if (g_static_k_scratch_ptr[h->device] == nullptr) {
+      // first call on this device: resolve the device address of the array (no allocation happens here)
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_k_scratch);
+      if (e != cudaSuccess || ptr == nullptr)
+        return fail(h, KREA_CUDA_E_CUDA, "joint_attention_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      g_static_k_scratch_ptr[h->device] = ptr;
+    }
+    scratch = g_static_k_scratch_ptr[h->device];
+  }
+  if (a->Lk == 0) {
+    AttnCall c{};
+    c.Q = a->Q; c.O = a->O; c.batch = a->batch <= 0 ? 1 : a->batch; c.Lq = a->Lq; c.Lk = 0; c.heads = a->heads; c.group = a->group;
+    c.ldq = a->ldq; c.ldk = c.ldv = (int64_t)(a->heads / a->group) * 128; c.ldo = a->ldo; c.bsq = a->bsq; c.bso = a->bso;
+    c.K = c.V = a->Q;
+    return run_attention(h, c);
+  }
+  // Every element of the scratch that the attention kernel reads is written by the pre-pass of this same
+  // call, so nothing has to be cleared between calls.
+  return joint_on_device(h, a, scratch);
 }
 
 static int stage_buf(krea_cuda* h, int slot, size_t bytes, void** out) {

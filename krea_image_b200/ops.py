@@ -113,6 +113,16 @@ class KreaCuda:
                              k_scratch_bytes)
         self._check(self.lib.krea_cuda_joint_attention(self.h, ctypes.byref(a)))
 
+    def joint_attention_static(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps=1e-6, group=1,
+                               rope_mode=B.ROPE_PAIRS, q_row0=0, *, batch=1, bsq=0, bsk=0, bsv=0, bso=0, text_len=None,
+                               text_slots=0, G=None, ldg=0, bsg=0):
+        """joint_attention for callers that may not allocate device memory: the normalised K goes to the
+        library's built-in 32 MiB device array (shared by every call on the device - do not overlap calls),
+        so problems with batch * Lk * kv_heads * 256 bytes above that size are refused with E_NOMEM."""
+        a = self._joint_args(Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps, group, rope_mode,
+                             q_row0, batch, bsq, bsk, bsv, bso, text_len, text_slots, G, ldg, bsg, None, 0)
+        self._check(self.lib.krea_cuda_joint_attention_static(self.h, ctypes.byref(a)))
+
     def joint_attention_host(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps=1e-6, group=1,
                              rope_mode=B.ROPE_PAIRS, q_row0=0, *, batch=1, bsq=0, bsk=0, bsv=0, bso=0, text_len=None,
                              text_slots=0):

@@ -1,0 +1,72 @@
+"""GPU test of krea_cuda_joint_attention_static, the fused call for callers that cannot allocate device
+memory (all memory already owned by another allocator, latency-critical paths that cannot afford
+cudaMalloc's device-wide synchronisation, hosts that forbid allocation after start-up).  It keeps the
+normalised K in a fixed array inside the library instead of scratch obtained at run time.
+
+Checked here, through the C ABI: its output equals the allocating entry point's bit for bit (same
+kernels, same data) on two calls in a row with different inputs - the second call finds the first call's
+contents in the shared array - and a problem larger than the built-in array is refused before anything
+is launched.  This file sorts last on purpose, so a run that stops at the first failure has already
+run every other test."""
+import numpy as np
+import pytest
+import torch
+
+from krea_image_b200 import binding, ops, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(seed, B, S, H, T, gh, gw):
+    rng = np.random.default_rng(seed)
+    qkv = synth.f32_to_bf16_bits(rng.standard_normal((B, S, 3 * H * 128)).astype(np.float32))
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    cos, sin = synth.rope_tables_axial2d(T, gh, gw)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    x = torch.from_numpy(qkv.view(np.int16)).cuda().view(torch.bfloat16).view(-1)
+    return x, dev(wq), dev(wk), dev(cos), dev(sin)
+
+
+def test_static_scratch_entry_matches_allocating_entry_twice():
+    kc = ops.KreaCuda(0)
+    kc.set_stream(torch.cuda.current_stream())
+    try:
+        for seed, (B, S, H, T, gh, gw), tl in ((1, (2, 600, 4, 88, 16, 32), [40, 88]), (2, (1, 1536, 6, 512, 32, 32), None)):
+            x, wq, wk, cos, sin = _case(seed, B, S, H, T, gh, gw)
+            ld = 3 * H * 128
+            lens = None if tl is None else torch.tensor(tl, dtype=torch.int32, device="cuda")
+            kw = dict(batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=lens, text_slots=T if tl else 0)
+            args = (S, S, H, ld, ld, ld, H * 128, wq, wk, cos, sin, 1e-6, 1, 0, 0)
+            want = torch.zeros((B, S, H * 128), dtype=torch.bfloat16, device="cuda")
+            kc.joint_attention(x, x[H * 128:], x[2 * H * 128:], want, *args, **kw)
+            kc.wait()
+            got = torch.full((B, S, H * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+            n0 = kc.launches
+            kc.joint_attention_static(x, x[H * 128:], x[2 * H * 128:], got, *args, **kw)
+            kc.wait()
+            assert kc.launches - n0 == 2
+            # same tolerance as the other parity tests would allow, but the two paths run the same kernels on
+            # the same data, so the results are identical
+            d = got.float() - want.float()
+            assert torch.isfinite(got.float()).all()
+            assert float(d.norm() / want.float().norm()) <= 5e-3 and float(d.abs().max()) <= 2e-2
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    finally:
+        kc.close()
+
+
+def test_static_scratch_entry_rejects_oversized_problem():
+    kc = ops.KreaCuda(0)
+    try:
+        H, S = 24, 6000      # 6000 keys x 24 heads x 256 B = 36.9 MB > 32 MiB
+        assert kc.joint_scratch_bytes(S, H) > binding.STATIC_SCRATCH_BYTES
+        t = torch.zeros(8, dtype=torch.bfloat16, device="cuda")   # never dereferenced: the call must be refused first
+        f = torch.zeros(128, device="cuda")
+        n0 = kc.launches
+        with pytest.raises(ops.KreaCudaError) as e:
+            kc.joint_attention_static(t, t, t, t, S, S, H, 3 * H * 128, 3 * H * 128, 3 * H * 128, H * 128, f, f, f, f)
+        assert e.value.code == binding.E_NOMEM and "exceed" in str(e.value)
+        assert kc.launches == n0
+    finally:
+        kc.close()

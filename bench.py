@@ -35,7 +35,7 @@ from krea_image_b200 import synth  # noqa: E402
 
 METRIC = "joint-attn TFLOP/s at S=4608 (1024^2), 24 heads, head_dim 128"
 FALLBACK_PEAK_TFLOPS = 1590.0
-WORKLOADS = {"c0": 0, "c1": 1, "c2": 2, "c3": 3}
+WORKLOADS = {"c0": 0, "c1": 1, "c2": 2, "c3": 3, "c4": 4}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at config 1, from the ncu capture
 # summarised under profiles/ (None until measured)
 ATTN_DRAM_TRAFFIC_BYTES = {1: None}
@@ -142,12 +142,90 @@ def run_reference(args, rank, world):
     }))
 
 
+def run_seq_parallel(args, rank, world, local_rank):
+    """--workload c4: the long-sequence configuration, strong scaling.  Rows start sequence-sharded over the
+    ranks; every step reshards Q, K, V to heads with an all-to-all, runs the fused call on full sequences
+    and brings the output rows back (at N=1 there is nothing to exchange: the fused call alone)."""
+    import torch
+    import torch.distributed as dist
+
+    from krea_image_b200 import dist as kd
+    from krea_image_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    cfg = synth.CONFIGS[4]
+    S, H = cfg.seq, cfg.heads
+    ld = 3 * H * 128
+    kc = ops.KreaCuda(local_rank)
+    stream = torch.cuda.current_stream()
+    kc.set_stream(stream)
+    plan = kd.UlyssesPlan(S, H, world)
+    lo, hi = plan.row_range(rank)
+    x = torch.from_numpy(synth.qkv_slice(cfg, row0=lo, nrows=hi - lo)[0].view(np.int16)).cuda().view(torch.bfloat16)
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = ops.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_wq, d_wk, d_cos, d_sin = dev(wq), dev(wk), dev(cos), dev(sin)
+    flops = synth.attention_flops(cfg)
+    if world > 1:
+        ua = kd.UlyssesAttention(kc, plan, kd.TorchGroup())
+        step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
+    else:
+        o = torch.empty((S, H * 128), dtype=torch.bfloat16, device="cuda")
+        xf = x.view(-1)
+        step = lambda: kc.joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o, S, S, H, ld, ld, ld, H * 128, d_wq, d_wk, d_cos, d_sin)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    kc.wait()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    n0 = kc.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    launches = kc.launches - n0
+    kc.wait()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, _, peak_kind = measured_peaks()
+        value = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "joint-attn TFLOP/s at S=66048 (4096^2), 24 heads, head_dim 128, sequence-parallel", "value": value,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": cfg.name, "batch": 1, "heads": H, "seq": S, "head_dim": 128,
+                       "parallelism": f"sequence-sharded in/out, all-to-all to {H // world} heads per GPU" if world > 1 else "single GPU",
+                       "l2": "inputs (1.2 GB) exceed the 126 MB L2"},
+            "pct_of_measured_bf16_peak": 100.0 * value / world / peak, "gpu_launches": int(launches), "clocks": clocks,
+            "e2e": None, "roofline": None}))
+    kc.close()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
 
     from krea_image_b200 import ops
 
+    if args.workload == "c4":
+        return run_seq_parallel(args, rank, world, local_rank)
     torch.cuda.set_device(local_rank)
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
     B, S, H = cfg.batch, cfg.seq, cfg.heads

@@ -82,11 +82,12 @@ class TorchGroup:
 def seq_to_heads(plan: UlyssesPlan, comm, x_local, col0: int, pack, alloc):
     """One of Q / K / V: x_local [rows_local, ld] holds all heads at columns [col0, col0 + heads*128).
     Returns [seq, cols_local]: every row of the sequence, this rank's heads.
-    pack(src, dst, nranks, rows, cols_per_rank, src_ld, src_col0) fills dst [P][rows][cols_per_rank]."""
+    pack(src, dst, nranks, rows, cols_per_rank, src_ld, src_col0) fills dst [P][rows][cols_per_rank];
+    alloc(shape, name) returns a (reusable) buffer: distinct names never alias."""
     P, rl, cl = plan.nranks, plan.rows_local, plan.cols_local
-    send = alloc((P, rl, cl))
+    send = alloc((P, rl, cl), "send")
     pack(x_local, send, P, rl, cl, x_local.shape[-1], col0)
-    recv = alloc((P, rl, cl))
+    recv = alloc((P, rl, cl), "recv")
     comm.all_to_all(recv, send)
     return recv.view(plan.seq, cl)   # block p holds rows [p*rl, (p+1)*rl): already in sequence order
 
@@ -95,9 +96,9 @@ def heads_to_seq(plan: UlyssesPlan, comm, o_heads, unpack, alloc):
     """o_heads [seq, cols_local] -> [rows_local, heads*128] (this rank's rows, all heads).
     unpack(src, dst, nranks, rows, cols_per_rank, dst_ld, dst_col0) merges src [P][rows][cols] into columns."""
     P, rl, cl = plan.nranks, plan.rows_local, plan.cols_local
-    recv = alloc((P, rl, cl))
+    recv = alloc((P, rl, cl), "recv")
     comm.all_to_all(recv, o_heads.view(P, rl, cl))   # row block p goes to rank p as it is
-    out = alloc((rl, plan.heads * HEAD_DIM))
+    out = alloc((rl, plan.heads * HEAD_DIM), "out")
     unpack(recv, out, P, rl, cl, plan.heads * HEAD_DIM, 0)
     return out
 
@@ -114,8 +115,8 @@ class UlyssesAttention:
     def _alloc(self, tag):
         torch = self.torch
 
-        def alloc(shape):
-            key = (tag, tuple(shape))
+        def alloc(shape, name):
+            key = (tag, name, tuple(shape))
             if key not in self._bufs:
                 self._bufs[key] = torch.empty(shape, dtype=torch.bfloat16, device=f"cuda:{self.kc.device}")
             return self._bufs[key]
@@ -130,7 +131,7 @@ class UlyssesAttention:
         parts = [seq_to_heads(plan, self.comm, qkv_local, t * H * HEAD_DIM, kc.reshard_pack, self._alloc(f"x{t}"))
                  for t in range(3)]
         q, k, v = parts
-        o = self._alloc("o")((plan.seq, plan.cols_local))
+        o = self._alloc("o")((plan.seq, plan.cols_local), "heads")
         cl = plan.cols_local
         kc.joint_attention(q, k, v, o, plan.seq, plan.seq, plan.heads_local, cl, cl, cl, cl, wq, wk, cos, sin, eps,
                            1, rope_mode)

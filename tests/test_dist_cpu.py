@@ -40,7 +40,7 @@ def _worker(rank, world, port, S, H):
         full = torch.randn(S, 3 * H * 128, generator=g).to(torch.bfloat16)      # same on every rank
         lo, hi = plan.row_range(rank)
         local = full[lo:hi].contiguous()
-        alloc = lambda shape: torch.empty(shape, dtype=torch.bfloat16)
+        alloc = lambda shape, name: torch.empty(shape, dtype=torch.bfloat16)
         h0, h1 = kd.head_range(H, world, rank)
         parts = []
         for t in range(3):

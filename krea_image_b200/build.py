@@ -36,14 +36,17 @@ def _stale() -> bool:
 
 
 def _check_register_budget(ptxas_log: str) -> None:
-    """The two-tile attention kernel re-balances registers between warpgroups with setmaxnreg: 8 warps go
-    up to 192 and 8 go down to 64, which only adds up (and can only be granted) if the CTA starts with
-    exactly 128 registers per thread.  A different launch count would leave the softmax warps waiting for
-    registers that never come, so refuse to build such a library."""
+    """The attention kernel re-balances registers between warpgroups with setmaxnreg: the softmax warps go
+    up and the producer / MMA warpgroup goes down, which only adds up (and can only be granted) if the CTA
+    starts with exactly the count the kernel's configuration assumes (168 per thread for the 384-thread
+    variant, 96 for the 640-thread one).  A different launch count would leave the softmax warps waiting
+    for registers that never come, so refuse to build such a library."""
     import re
-    for m in re.finditer(r"Compiling entry function '(\w*attn_fwd_sm100ILi2\w*)'.*?Used (\d+) registers", ptxas_log, re.S):
-        if int(m.group(2)) != 128:
-            raise RuntimeError(f"{m.group(1)} starts with {m.group(2)} registers per thread; setmaxnreg needs 128")
+    expect = {"1": 168, "2": 96}
+    for m in re.finditer(r"Compiling entry function '(\w*attn_fwd_sm100ILi(\d)\w*)'.*?Used (\d+) registers", ptxas_log, re.S):
+        want = expect.get(m.group(2))
+        if want is not None and int(m.group(3)) != want:
+            raise RuntimeError(f"{m.group(1)} starts with {m.group(3)} registers per thread; setmaxnreg needs {want}")
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

@@ -31,8 +31,11 @@
 // Optional phase trace for tuning builds (-DKREA_ATTN_TRACE): CTA 0 records clock64() at the points
 // marked KTRACE into p.trace; compiled out otherwise.
 #ifdef KREA_ATTN_TRACE
+#ifndef KTRACE_Y
+#define KTRACE_Y 0
+#endif
 #define KTRACE(cond, slot, j) \
-  do { if ((cond) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.trace && (j) < 64) p.trace[(slot) * 64 + (j)] = clock64(); } while (0)
+  do { if ((cond) && blockIdx.x == 0 && blockIdx.y == KTRACE_Y && blockIdx.z == 0 && p.trace && (j) < 64) p.trace[(slot) * 64 + (j)] = clock64(); } while (0)
 #else
 #define KTRACE(cond, slot, j) do { } while (0)
 #endif
@@ -42,6 +45,7 @@ namespace krea {
 constexpr int D = 128;               // head_dim
 constexpr int BM = 128;              // query rows per tile (= TMEM lanes)
 constexpr int BN = 128;              // keys per tile
+constexpr int NQ = 2;                // query tiles per CTA
 constexpr int TILE_BYTES = BN * D * 2;       // 32 KB: one K or V tile, or one Q tile
 constexpr int HALF_BYTES = TILE_BYTES / 2;   // two 64-column halves, each 128 rows x 128 B
 constexpr int NSTAGE = 4;            // K/V ring depth (K_j and V_j take one stage each)
@@ -53,15 +57,38 @@ constexpr float kMaxStaticBound = 40.0f;
 // wait sites (reported in the status word)
 enum : uint32_t { SITE_Q = 1, SITE_KV_FULL = 2, SITE_KV_EMPTY = 3, SITE_S = 4, SITE_P = 5, SITE_PV = 6, SITE_DRAIN = 7 };
 
-template <int NQ>
 struct SmemLayout {
   static constexpr int q_off = 0;
   static constexpr int kv_off = NQ * TILE_BYTES;
   static constexpr int bar_off = kv_off + NSTAGE * TILE_BYTES;
   // barriers: q_ready[NQ], s_full[NQ], p_full[NQ], pv_done[NQ], kv_full[NSTAGE], kv_empty[NSTAGE], s_free
   static constexpr int n_bars = 4 * NQ + 2 * NSTAGE + 1;
-  static constexpr int misc_off = bar_off + n_bars * 8;
-  static constexpr int total = misc_off + 16;
+  static constexpr int misc_off = bar_off + n_bars * 8;            // tmem slot, abort words
+  static constexpr int xchg_off = misc_off + 16;                   // row-max exchange: f32 [2 buffers][NQ][128][2]
+  static constexpr int lsum_off = xchg_off + 2 * NQ * 128 * 2 * 4; // row-sum exchange: f32 [NQ][128][2]
+  static constexpr int total = lsum_off + NQ * 128 * 2 * 4;
+};
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Thread layout: warps [0, 4*SPLIT) are the softmax warps of query tile 0, the next 4*SPLIT those of tile
+// 1, then one warpgroup whose warp 0 is the TMA producer and warp 1 the MMA issuer.  Softmax warp w of a
+// tile owns TMEM lanes (rows) 32*(w%4) .. +31 and key columns (128/SPLIT)*(w/4) .. of every score tile:
+// with SPLIT = 2 a row is shared by two threads and four softmax warps per scheduler hide each other's
+// special-function and TMEM latencies.  The softmax warps take registers from the last warpgroup with
+// setmaxnreg; the CTA must start with exactly REGS_LAUNCH per thread for the two requests to add up.
+template <int SPLIT>
+struct Cfg {
+  static constexpr int SM_WARPS = 4 * SPLIT;            // softmax warps per query tile
+  static constexpr int SM_THREADS = 128 * SPLIT;
+  static constexpr int THREADS = NQ * SM_THREADS + 128;
+  static constexpr int COLS = BN / SPLIT;               // score columns per thread
+  static constexpr int REGS_SOFTMAX = SPLIT == 1 ? 216 : 104;   // 384 threads start at 168, 640 threads at 96
+  static constexpr int REGS_OTHER = SPLIT == 1 ? 72 : 64;
+  static constexpr int REGS_LAUNCH = (NQ * SM_THREADS * REGS_SOFTMAX + 128 * REGS_OTHER) / THREADS;
+  static_assert(REGS_LAUNCH * THREADS == NQ * SM_THREADS * REGS_SOFTMAX + 128 * REGS_OTHER, "register budget must add up");
 };
 
 // First / one-past-last fully masked key tile for padding range [lo, hi).
@@ -71,16 +98,15 @@ __device__ __forceinline__ void skip_range(int lo, int hi, int& first, int& end)
   if (end < first) end = first;
 }
 
-// Thread layout: warps [0, 4*NQ) softmax warpgroups (one per query tile), then one warpgroup whose
-// warp 0 is the TMA producer and warp 1 the MMA issuer.  The softmax warpgroups take registers from
-// the others with setmaxnreg.  EMU: how many of every four element pairs use the polynomial exp2.
-template <int NQ, int EMU>
-__global__ void __launch_bounds__(NQ * 128 + 128 + (NQ == 2 ? 128 : 0), 1)
+// EMU: how many of every four element pairs use the polynomial exp2.
+template <int SPLIT, int EMU>
+__global__ void __launch_bounds__(Cfg<SPLIT>::THREADS, 1)
 attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 B the swizzle needs
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  using L = SmemLayout<NQ>;
+  using C = Cfg<SPLIT>;
+  using L = SmemLayout;
   uint8_t* q_smem = smem + L::q_off;
   uint8_t* kv_smem = smem + L::kv_off;
   uint64_t* bars = (uint64_t*)(smem + L::bar_off);
@@ -93,6 +119,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   uint64_t* s_free = kv_empty + NSTAGE;
   uint32_t* tmem_slot = (uint32_t*)(smem + L::misc_off);
   volatile uint32_t* abort_word = (volatile uint32_t*)(smem + L::misc_off + 4);
+  float* xchg = (float*)(smem + L::xchg_off);
+  float* lsum_x = (float*)(smem + L::lsum_off);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -122,23 +150,24 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   // each softmax warpgroup always finds its next score tile ready and the tensor pipe never drains.
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_S = 0, COL_P = 128, COL_O = 256;
+  constexpr int WARP_TMA = NQ * C::SM_WARPS, WARP_MMA = WARP_TMA + 1;
   if (threadIdx.x == 0) {
     for (int g = 0; g < NQ; g++) {
-      mbar_init(&q_ready[g], 128);
+      mbar_init(&q_ready[g], C::SM_THREADS);
       mbar_init(&s_full[g], 1);
-      mbar_init(&p_full[g], 128);
+      mbar_init(&p_full[g], C::SM_THREADS);
       mbar_init(&pv_done[g], 1);
     }
     for (int s = 0; s < NSTAGE; s++) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_free, 128);
+    mbar_init(s_free, C::SM_THREADS);
     abort_word[0] = (p.status != nullptr && *p.status != 0u) ? 0xFFu : 0u;  // a failed launch poisons later CTAs
     abort_word[1] = 0u;                                                     // private word of the drain loop
     fence_mbar_init();
   }
-  if (warp == NQ * 4 + 1) {   // the MMA warp owns the TMEM allocation
+  if (warp == WARP_MMA) {   // the MMA warp owns the TMEM allocation
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -148,18 +177,21 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
   KTRACE(threadIdx.x == 0, 30, 3);
 
-  constexpr int WARP_TMA = NQ * 4, WARP_MMA = NQ * 4 + 1;
-  if (warp < NQ * 4) {
-    // =============================== softmax / epilogue warpgroups ===============================
-    if constexpr (NQ == 2) reg_inc<192>();   // 8 warps x 192 + 8 warps x 64 = the 128 per thread the CTA starts with
-    const int g = warp >> 2;
-    const int r = (warp & 3) * 32 + lane;              // row inside the tile = TMEM lane
+  if (warp < NQ * C::SM_WARPS) {
+    // ==================================== softmax / epilogue warps ====================================
+    reg_inc<C::REGS_SOFTMAX>();
+    const int g = warp / C::SM_WARPS;                   // query tile
+    const int wt = warp % C::SM_WARPS;                  // warp inside the tile's set
+    const int part = wt >> 2;                           // which share of the key columns
+    const int r = (wt & 3) * 32 + lane;                 // row inside the tile = TMEM lane
     const int row = q0 + g * BM + r;
     const bool tile_active = (q0 + g * BM) < p.Lq;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t tS = lane_addr + COL_S;
-    const uint32_t tP = lane_addr + COL_P + (uint32_t)(g * 64);
-    const uint32_t tO = lane_addr + COL_O + (uint32_t)(g * D);
+    const bool trace_me = threadIdx.x == g * C::SM_THREADS;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((wt & 3) * 32) << 16);
+    const uint32_t tS = lane_addr + COL_S + (uint32_t)(part * C::COLS);
+    const uint32_t tP = lane_addr + COL_P + (uint32_t)(g * 64 + part * (C::COLS / 2));
+    const uint32_t tO = lane_addr + COL_O + (uint32_t)(g * D + part * (D / SPLIT));
+    const int bar_id = 1 + g;                           // named barrier of this tile's softmax warps
 
     if (tile_active && n_tiles > 0) {
       // ---- stage Q (with the fused RMSNorm + RoPE prologue when weights are given) ----
@@ -170,6 +202,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       {
         const int sub = lane >> 4, c = lane & 15;
         const __nv_bfloat16* qhead = p.Q + (size_t)b * p.bsq + (size_t)h * D + 8 * c;
+        constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;          // 32 or 16
         // MODE 0 / 1 / 2: RMSNorm + interleaved-pair / rotate-half / no RoPE; MODE 3: copy as it is.
         // Eight rows per lane are in flight at a time: all their global loads are issued before any of
         // them is used, so the staging costs about two memory round trips instead of sixteen.
@@ -181,14 +214,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
           }
 #pragma unroll 1
-          for (int half = 0; half < 2; half++) {
+          for (int batch = 0; batch < ROWS_PER_WARP / 16; batch++) {
             uint4 raw[8];
             float4 t0[8], t1[8];     // MODE 0: cos, sin of this chunk's 4 pairs; MODE 1: cos (2 x float4 in t0/t1)
             float4 t2[8], t3[8];     // MODE 1: sin
             int rr[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-              rr[i] = (warp & 3) * 32 + (half * 8 + i) * 2 + sub;       // row inside the tile
+              rr[i] = wt * ROWS_PER_WARP + (batch * 8 + i) * 2 + sub;  // row inside the tile
               const int grow = min(q0 + g * BM + rr[i], p.Lq - 1);     // rows past Lq are clamped, never stored
               raw[i] = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
               const size_t trow = (size_t)(p.q_row0 + grow) * 64;
@@ -258,7 +291,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         fence_proxy_async_smem();
         mbar_arrive(&q_ready[g]);
       }
-      KTRACE(threadIdx.x == g * 128, 30 + g, 0);
+      KTRACE(trace_me, 30 + g, 0);
 
       // ---- softmax over the key tiles ----
       // Two forms of the same math.  Online: running row max, moved lazily (only when exceeded by more
@@ -274,25 +307,23 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         constexpr bool BOUNDED = decltype(bounded_tag)::value;
         for (int j = 0; j < n_tiles; j++) {
           const int kt = tile_of(j);
-          const int key0 = kt * BN;
-          KTRACE(threadIdx.x == g * 128, g * 8 + 0, j);
+          const int key0 = kt * BN + part * C::COLS;       // first key of this thread's columns
+          KTRACE(trace_me, g * 8 + 0, j);
           mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
           tc_fence_after();
-          KTRACE(threadIdx.x == g * 128, g * 8 + 1, j);
-          uint32_t sv[128];
-          tmem_ld32(tS + 0, sv + 0);
-          tmem_ld32(tS + 32, sv + 32);
-          tmem_ld32(tS + 64, sv + 64);
-          tmem_ld32(tS + 96, sv + 96);
+          KTRACE(trace_me, g * 8 + 1, j);
+          uint32_t sv[C::COLS];
+#pragma unroll
+          for (int c0 = 0; c0 < C::COLS; c0 += 32) tmem_ld32(tS + c0, sv + c0);
           tmem_wait_ld();
           tc_fence_before();
           mbar_arrive(s_free);     // the scores are in registers: the next Q K^T may overwrite the tile
-          KTRACE(threadIdx.x == g * 128, g * 8 + 2, j);
+          KTRACE(trace_me, g * 8 + 2, j);
           float* s = (float*)sv;
-          const bool need_mask = (key0 + BN > p.Lk) || (key0 < pad_hi && key0 + BN > pad_lo);
+          const bool need_mask = (kt * BN + BN > p.Lk) || (kt * BN < pad_hi && kt * BN + BN > pad_lo);
           if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < 128; c++) {
+            for (int c = 0; c < C::COLS; c++) {
               const int key = key0 + c;
               const bool ok = key < p.Lk && !(key >= pad_lo && key < pad_hi);
               s[c] = ok ? s[c] : -INFINITY;
@@ -307,11 +338,21 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             // row max: four independent chains of 3-input max
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 4; c < 128; c += 8) {
+            for (int c = 4; c + 7 < C::COLS; c += 8) {
 #pragma unroll
               for (int u = 0; u < 4; u++) mx4[u] = max3(mx4[u], s[c + 2 * u], s[c + 2 * u + 1]);
             }
-            const float lm = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            mx = fmaxf(fmaxf(mx, s[C::COLS - 4]), fmaxf(s[C::COLS - 3], fmaxf(s[C::COLS - 2], s[C::COLS - 1])));
+            if constexpr (SPLIT == 2) {
+              // the rest of the row belongs to the thread of the warp four further on: exchange through
+              // shared memory (two buffers, alternating per tile, make one barrier per tile enough)
+              float* slot = xchg + (((j & 1) * NQ + g) * 128 + r) * 2;
+              slot[part] = mx;
+              named_barrier(bar_id, C::SM_THREADS);
+              mx = fmaxf(mx, slot[part ^ 1]);
+            }
+            const float lm = mx * sc2;
             const bool need = lm > m_i + LAZY_TH;   // first tile: m_i = -inf
             if (__any_sync(0xffffffffu, need)) {
               const float m_new = need ? lm : m_i;
@@ -323,7 +364,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
             m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
           }
-          KTRACE(threadIdx.x == g * 128, g * 8 + 3, j);
+          KTRACE(trace_me, g * 8 + 3, j);
           if (j > 0) {
             // P V of the previous key tile still reads P_g (and, for a rescale, writes O_g) until this completes
             mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
@@ -335,7 +376,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           const uint64_t sc2x2 = pack_f32x2(sc2, sc2), negm2 = pack_f32x2(-m_use, -m_use);
           uint64_t lsum2[2] = {0ull, 0ull};
 #pragma unroll
-          for (int ch = 0; ch < 4; ch++) {
+          for (int ch = 0; ch < C::COLS / 32; ch++) {
             uint64_t x2[16];
 #pragma unroll
             for (int i = 0; i < 16; i++) x2[i] = fma_f32x2(pack_f32x2(s[ch * 32 + 2 * i], s[ch * 32 + 2 * i + 1]), sc2x2, negm2);
@@ -366,12 +407,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             unpack_f32x2(lsum2[1], b0, b1);
             l_i += (a0 + a1) + (b0 + b1);
           }
-          KTRACE(threadIdx.x == g * 128, g * 8 + 4, j);
+          KTRACE(trace_me, g * 8 + 4, j);
           if (rescale) {
             // the running max moved: rescale this row of O before P V of this tile may accumulate into it
             // (P V of the previous tile has landed: see the wait above)
 #pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < D / SPLIT; c0 += 32) {
               uint32_t ov[32];
               tmem_ld32(tO + c0, ov);
               tmem_wait_ld();
@@ -381,7 +422,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
           }
           tmem_wait_st();
-          KTRACE(threadIdx.x == g * 128, g * 8 + 5, j);
+          KTRACE(trace_me, g * 8 + 5, j);
           tc_fence_before();
           mbar_arrive(&p_full[g]);
         }
@@ -389,27 +430,33 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (bound <= kMaxStaticBound) softmax_tiles(std::true_type{});
       else softmax_tiles(std::false_type{});
 
-      KTRACE(threadIdx.x == g * 128, 30 + g, 1);
+      KTRACE(trace_me, 30 + g, 1);
       // ---- epilogue: O / l (x sigmoid(G)) -> bf16, staged through shared memory for coalesced stores ----
       // Each thread owns one row in TMEM, but a row is 256 contiguous bytes in global memory: the tile is
       // first written to the (now idle) Q buffer of this tile, 16-byte chunk c of row r in chunk slot
       // c ^ (r & 15), and then stored with 16 lanes per row so that every store instruction of a warp
       // writes two full 256-byte rows.
+      if constexpr (SPLIT == 2) {
+        // the row sum is the sum of the two threads' shares
+        float* slot = lsum_x + (g * 128 + r) * 2;
+        slot[part] = l_i;
+        named_barrier(bar_id, C::SM_THREADS);
+        l_i += slot[part ^ 1];
+      }
       mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV);
       tc_fence_after();
-      KTRACE(threadIdx.x == g * 128, 30 + g, 4);
+      KTRACE(trace_me, 30 + g, 4);
       const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
       const int pos = p.q_row0 + row;
       const bool padded_row = pos >= pad_lo && pos < pad_hi;
       const int rs = min(row, p.Lq - 1);
-      const uint4* gsrc = p.G ? (const uint4*)(p.G + (size_t)b * p.bsg + (size_t)rs * p.ldg + (size_t)h * D) : nullptr;
+      const uint4* gsrc = p.G ? (const uint4*)(p.G + (size_t)b * p.bsg + (size_t)rs * p.ldg + (size_t)h * D) + part * (16 / SPLIT) : nullptr;
       uint8_t* ostage = q_smem + g * TILE_BYTES;
 #pragma unroll 1   // executed once per CTA: compact code beats unrolled code that has to be fetched cold
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < D / SPLIT; c0 += 32) {
         uint32_t ov[32];
         tmem_ld32(tO + c0, ov);
         tmem_wait_ld();
-        KTRACE(threadIdx.x == g * 128, 32 + g, 2 * (c0 >> 5));
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
           float f[8];
@@ -424,34 +471,34 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
               f[2 * e + 1] *= 1.0f / (1.0f + __expf(-bf16hi_to_f32(g4[e])));
             }
           }
-          const int ch = (c0 >> 3) + q4;
+          const int ch = part * (16 / SPLIT) + (c0 >> 3) + q4;
           *(uint4*)(ostage + r * 256 + ((ch ^ (r & 15)) << 4)) =
               make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
         }
-        KTRACE(threadIdx.x == g * 128, 32 + g, 2 * (c0 >> 5) + 1);
       }
-      KTRACE(threadIdx.x == g * 128, 30 + g, 5);
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");   // the 128 threads of this warpgroup
+      KTRACE(trace_me, 30 + g, 5);
+      named_barrier(bar_id, C::SM_THREADS);   // all softmax warps of this tile
       {
         const int sub = lane >> 4, ch = lane & 15;
+        constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;
         __nv_bfloat16* obase = p.O + (size_t)b * p.bso + (size_t)h * D + 8 * ch;
 #pragma unroll 4
-        for (int it = 0; it < 16; it++) {
-          const int rr = (warp & 3) * 32 + it * 2 + sub;
+        for (int it = 0; it < ROWS_PER_WARP / 2; it++) {
+          const int rr = wt * ROWS_PER_WARP + it * 2 + sub;
           const int grow = q0 + g * BM + rr;
           const uint4 v = *(const uint4*)(ostage + rr * 256 + ((ch ^ (rr & 15)) << 4));
           if (grow < p.Lq) *(uint4*)(obase + (size_t)grow * p.ldo) = v;
         }
       }
-      KTRACE(threadIdx.x == g * 128, 30 + g, 2);
-    } else if (tile_active && row < p.Lq) {
+      KTRACE(trace_me, 30 + g, 2);
+    } else if (tile_active && row < p.Lq && part == 0) {
       // no visible key at all: zeros
       uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)row * p.ldo + (size_t)h * D);
 #pragma unroll
       for (int c = 0; c < 16; c++) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     }
   } else {
-    if constexpr (NQ == 2) reg_dec<64>();
+    reg_dec<C::REGS_OTHER>();
     if (warp == WARP_TMA) {
     // ======================================= TMA producer =======================================
     if (lane == 0 && n_tiles > 0) {
@@ -498,30 +545,37 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const uint32_t kv_lo = smem_u32(kv_smem) >> 4;
       constexpr uint32_t TILE16 = TILE_BYTES >> 4, HALF16 = HALF_BYTES >> 4;
 
+      // Descriptors and addresses are computed by the whole (converged) warp so that the arithmetic
+      // can stay on the warp-uniform datapath; only the asynchronous instruction itself is predicated
+      // on the elected lane.
+      const uint32_t d_s = tmem_base + COL_S;
       auto issue_qk = [&](int g, int stage) {
         const uint32_t qa = q_lo + g * TILE16, kb = (kv_lo + stage * TILE16) | LBO_K;
-        if (leader) {
 #pragma unroll
-          for (int k = 0; k < 8; k++) {
-            const uint32_t off = (k >> 2) * HALF16 + (k & 3) * 2;     // 16 channels = 32 B per step inside a 128 B row
-            if (k == 0) umma_ss<false>(tmem_base + COL_S, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
-            else umma_ss<true>(tmem_base + COL_S, make_desc(qa + off, HI), make_desc(kb + off, HI), idesc_qk);
+        for (int k = 0; k < 8; k++) {
+          const uint32_t off = (k >> 2) * HALF16 + (k & 3) * 2;       // 16 channels = 32 B per step inside a 128 B row
+          const uint64_t da = make_desc(qa + off, HI), db = make_desc(kb + off, HI);
+          if (leader) {
+            if (k == 0) umma_ss<false>(d_s, da, db, idesc_qk);
+            else umma_ss<true>(d_s, da, db, idesc_qk);
           }
-          umma_commit(&s_full[g]);
         }
+        if (leader) umma_commit(&s_full[g]);
         __syncwarp();
       };
       auto issue_pv = [&](int g, int stage, bool first) {
         const uint32_t vb = (kv_lo + stage * TILE16) | LBO_V;
         const uint32_t d_o = tmem_base + COL_O + g * D, a_p = tmem_base + COL_P + g * 64;
         // 16 keys per MMA: A = 8 packed-bf16 columns of P in TMEM, B = 16 rows (2048 B) of the V stage
-        if (leader) {
-          if (first) umma_ts<false>(d_o, a_p, make_desc(vb, HI), idesc_pv);
-          else umma_ts<true>(d_o, a_p, make_desc(vb, HI), idesc_pv);
 #pragma unroll
-          for (int k = 1; k < 8; k++) umma_ts<true>(d_o, a_p + k * 8, make_desc(vb + k * 128, HI), idesc_pv);
-          umma_commit(&pv_done[g]);
+        for (int k = 0; k < 8; k++) {
+          const uint64_t db = make_desc(vb + k * 128, HI);
+          if (leader) {
+            if (k == 0 && first) umma_ts<false>(d_o, a_p, db, idesc_pv);
+            else umma_ts<true>(d_o, a_p + k * 8, db, idesc_pv);
+          }
         }
+        if (leader) umma_commit(&pv_done[g]);
         __syncwarp();
       };
 
@@ -581,7 +635,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == NQ * 4 + 1) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
@@ -591,30 +645,25 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   }
 }
 
-template <int NQ, int EMU>
+template <int SPLIT, int EMU>
 static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, cudaStream_t stream) {
-  const int smem = SmemLayout<NQ>::total + 1024;
+  const int smem = SmemLayout::total + 1024;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<NQ, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<SPLIT, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   dim3 grid((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
-  attn_fwd_sm100<NQ, EMU><<<grid, NQ * 128 + 128 + (NQ == 2 ? 128 : 0), smem, stream>>>(tmK, tmV, p);
+  attn_fwd_sm100<SPLIT, EMU><<<grid, Cfg<SPLIT>::THREADS, smem, stream>>>(tmK, tmV, p);
   return cudaGetLastError();
 }
 
-cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int nq, int emu, cudaStream_t stream) {
-  if (nq == 1) return launch_impl<1, 0>(tmK, tmV, p, stream);
-  switch (emu) {
-    case 0: return launch_impl<2, 0>(tmK, tmV, p, stream);
-    case 2: return launch_impl<2, 2>(tmK, tmV, p, stream);
-    case 3: return launch_impl<2, 3>(tmK, tmV, p, stream);
-    default: return launch_impl<2, 1>(tmK, tmV, p, stream);
-  }
+cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int split, int emu, cudaStream_t stream) {
+  if (split == 1) return emu == 1 ? launch_impl<1, 1>(tmK, tmV, p, stream) : launch_impl<1, 0>(tmK, tmV, p, stream);
+  return emu == 1 ? launch_impl<2, 1>(tmK, tmV, p, stream) : launch_impl<2, 0>(tmK, tmV, p, stream);
 }
 
 }  // namespace krea

@@ -35,9 +35,9 @@ struct AttnParams {
 };
 
 // K and V are described by 3-D tensor maps (column, row, sample) with 64-column x 128-row boxes and
-// 128-byte swizzle.  nq = query tiles of 128 rows per CTA (1 or 2); emu = how many of every four
-// element pairs evaluate exp2 with the FMA-pipe polynomial instead of the special-function unit (0-3).
-cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int nq, int emu, cudaStream_t stream);
+// 128-byte swizzle.  split = threads per query row in the softmax (1 or 2); emu = 1 lets one of every four
+// element pairs evaluate exp2 with the FMA-pipe polynomial instead of the special-function unit.
+cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int split, int emu, cudaStream_t stream);
 
 // Out-of-place / in-place per-head RMSNorm + RoPE (qk_norm_rope.cu).
 struct NormRopeParams {

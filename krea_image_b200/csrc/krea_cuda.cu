@@ -37,8 +37,8 @@ struct krea_cuda {
   size_t stage_bytes[8] = {};
   uint64_t launches = 0;
   PFN_encodeTiled encode = nullptr;
-  int nq = 2;                       // query tiles per CTA
-  int emu = 0;                      // of every 4 element pairs, how many take the polynomial exp2
+  int split = 1;                    // softmax threads per query row
+  int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
   bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
   bool profiling = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
@@ -134,14 +134,14 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     return nullptr;
   }
   h->stream = h->own_stream;
-  if (const char* s = getenv("KREA_CUDA_NQ")) {  // tuning knob: 1 or 2 query tiles per CTA
+  if (const char* s = getenv("KREA_CUDA_SPLIT")) {  // tuning knob: 1 or 2 softmax threads per query row
     const int v = atoi(s);
-    if (v == 1 || v == 2) h->nq = v;
+    if (v == 1 || v == 2) h->split = v;
   }
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);
-    if (v >= 0 && v <= 3) h->emu = v;
+    if (v >= 0 && v <= 1) h->emu = v;
   }
   return h;
 }
@@ -339,11 +339,9 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
     rc = make_kv_map(h, &tmV, c.V, kvheads * 128, c.Lk, c.batch, c.ldv, c.bsv, "V");
     if (rc) return rc;
   }
-  // one 128-row tile per CTA when two would leave most SMs without work
-  int nq = h->nq;
   {
     ProfileMark pm(h, 1);
-    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, nq, h->emu, h->stream));
+    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, p, h->split, h->emu, h->stream));
   }
   h->launches++;
   return KREA_CUDA_OK;

@@ -17,6 +17,10 @@ struct AttnParams {
   int64_t bsq, bso, bsg;
   int Lq, Lk, heads, group, batch;
   float scale_log2;            // softmax scale * log2(e)
+  int causal, q_pos0;          // causal: key k visible to query row i iff k <= i + q_pos0
+  const float* QB;             // optional fp32 rank-1 score term QB[q, heads] * KB[k, heads/group] (no batch)
+  const float* KB;
+  int ldqb, ldkb;
   // fused Q prologue (nullptr wq = Q is used as it is)
   const float* wq;
   const float* cos;

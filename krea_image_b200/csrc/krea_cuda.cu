@@ -40,6 +40,10 @@ struct krea_cuda {
   int split = 1;                    // softmax threads per query row
   int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
   bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host entry point: H2D and D2H streams
+  cudaEvent_t pipe_ev[18] = {};                   // [0,8) group in, [8,16) group out, 16 start, 17 bounce
+  void* bounce = nullptr;           // pinned host staging for the small operands of the host entry point
+  size_t bounce_bytes = 0;
   bool profiling = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
   std::vector<cudaEvent_t> event_pool;
@@ -161,6 +165,11 @@ void krea_cuda_destroy(krea_cuda* h) {
       cudaEventDestroy(m.second);
     }
   for (cudaEvent_t e : h->event_pool) cudaEventDestroy(e);
+  for (int i = 0; i < 18; i++)
+    if (h->pipe_ev[i]) cudaEventDestroy(h->pipe_ev[i]);
+  if (h->bounce) cudaFreeHost(h->bounce);
+  if (h->copy_in) cudaStreamDestroy(h->copy_in);
+  if (h->copy_out) cudaStreamDestroy(h->copy_out);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
   delete h;
 }
@@ -296,6 +305,8 @@ struct AttnCall {
   const int32_t* text_len;
   int text_slots;
   const float* logit_bound;
+  int causal, q_pos0;
+  const float *QB, *KB;
 };
 
 static int run_attention(krea_cuda* h, const AttnCall& c) {
@@ -325,6 +336,8 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.bsq = c.bsq; p.bso = c.bso; p.bsg = c.bsg;
   p.Lq = c.Lq; p.Lk = c.Lk; p.heads = c.heads; p.group = c.group; p.batch = c.batch;
   p.scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);   // engine/src/metal.mm:198
+  p.causal = c.causal ? 1 : 0; p.q_pos0 = c.q_pos0;
+  p.QB = c.QB; p.KB = c.KB; p.ldqb = c.heads; p.ldkb = kvheads;      // row strides = heads and heads / group (metal.h:85)
   p.wq = c.wq; p.cos = c.cos; p.sin = c.sin; p.eps = c.eps; p.rope_mode = c.rope_mode; p.q_row0 = c.q_row0;
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
   p.logit_bound = (h->static_bound && c.wq) ? c.logit_bound : nullptr;
@@ -349,8 +362,9 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
 
 int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a) {
   if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "attention: null handle or arguments");
-  if (a->causal) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: causal masking (text-encoder caller) is not built");
-  if (a->QB || a->KB) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: the fp32 rank-1 score term (QB/KB) is not built");
+  const bool big = a->QB && a->KB;                                     // engine/src/metal.mm:196
+  if (big && a->batch > 1) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: QB/KB have no batch dimension");
+  if (a->causal && a->text_len) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention: causal masking and the text padding mask are not combined");
   AttnCall c{};
   c.Q = a->Q; c.K = a->K; c.V = a->V; c.O = a->O;
   c.G = (a->G && a->ldg > 0) ? a->G : nullptr;
@@ -361,6 +375,8 @@ int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a) {
   c.wq = nullptr; c.cos = c.sin = nullptr; c.eps = 0.f; c.rope_mode = KREA_CUDA_ROPE_NONE;
   c.q_row0 = a->q_row0;
   c.text_len = a->text_len; c.text_slots = a->text_slots;
+  c.causal = a->causal; c.q_pos0 = a->q_pos0;
+  c.QB = big ? a->QB : nullptr; c.KB = big ? a->KB : nullptr;
   return run_attention(h, c);
 }
 
@@ -549,37 +565,125 @@ int krea_cuda_joint_attention_host(krea_cuda* h, const krea_cuda_joint_args* a) 
   if ((rc = stage_buf(h, 4, (size_t)trows * 64 * 4 * 2, &dT))) return rc;
   if ((rc = stage_buf(h, 5, 1024, &dW))) return rc;
   if ((rc = stage_buf(h, 6, (size_t)batch * 4 + 16, &dL))) return rc;
-  for (int b = 0; b < batch; b++) {
-    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dQ + (size_t)b * a->Lq * qw * 2, qw * 2, (const char*)a->Q + (size_t)b * a->bsq * 2, (size_t)a->ldq * 2,
-                                  qw * 2, a->Lq, cudaMemcpyHostToDevice, h->stream));
-    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dK + (size_t)b * a->Lk * kw * 2, kw * 2, (const char*)a->K + (size_t)b * a->bsk * 2, (size_t)a->ldk * 2,
-                                  kw * 2, a->Lk, cudaMemcpyHostToDevice, h->stream));
-    CUDA_TRY(h, cudaMemcpy2DAsync((char*)dV + (size_t)b * a->Lk * kw * 2, kw * 2, (const char*)a->V + (size_t)b * a->bsv * 2, (size_t)a->ldv * 2,
-                                  kw * 2, a->Lk, cudaMemcpyHostToDevice, h->stream));
+  // Heads are independent, so the call is pipelined over groups of heads: while one group is being
+  // computed, the next group's columns of Q, K and V are still arriving over PCIe on a second stream and
+  // the previous group's output is already on its way back on a third (the two copy directions use
+  // different DMA engines).  The results are the same as one call over all heads.
+  int ngroups = 1;
+  const size_t total_in = (size_t)batch * ((size_t)a->Lq * qw + 2 * (size_t)a->Lk * kw) * 2;
+  if (total_in >= ((size_t)8 << 20)) {
+    for (int cand : {6, 4, 3, 2})   // narrower column blocks than about 1 KB per row slow the DMA down
+      if (kvheads % cand == 0) { ngroups = cand; break; }
+  }
+  if (!h->copy_in) {
+    CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
+    CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 18; i++) CUDA_TRY(h, cudaEventCreateWithFlags(&h->pipe_ev[i], cudaEventDisableTiming));
+  }
+  if (const char* e = getenv("KREA_CUDA_HOST_GROUPS")) {   // tuning knob
+    const int v = atoi(e);
+    if (v >= 1 && v <= 8 && kvheads % v == 0) ngroups = v;
+  }
+  const bool ttrace = getenv("KREA_CUDA_HOST_TRACE") != nullptr;   // tuning aid: print the pipeline's timeline
+  cudaEvent_t tev[32] = {};
+  if (ttrace) for (int i = 0; i < 32; i++) cudaEventCreate(&tev[i]);
+  const int kvh_g = kvheads / ngroups, hq_g = a->heads / ngroups;     // kv heads / query heads per group
+  const size_t qcw = (size_t)hq_g * 128 * 2, kcw = (size_t)kvh_g * 128 * 2;   // column-block widths in bytes
+  // order the copy streams after whatever the caller enqueued on the compute stream
+  CUDA_TRY(h, cudaEventRecord(h->pipe_ev[16], h->stream));
+  CUDA_TRY(h, cudaStreamWaitEvent(h->copy_in, h->pipe_ev[16], 0));
+  CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->pipe_ev[16], 0));
+  if (ttrace) cudaEventRecord(tev[0], h->copy_in);
+  for (int gi = 0; gi < ngroups; gi++) {
+    for (int b = 0; b < batch; b++) {
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dQ + (size_t)b * a->Lq * qw * 2 + gi * qcw, qw * 2,
+                                    (const char*)a->Q + (size_t)b * a->bsq * 2 + gi * qcw, (size_t)a->ldq * 2, qcw, a->Lq,
+                                    cudaMemcpyHostToDevice, h->copy_in));
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dK + (size_t)b * a->Lk * kw * 2 + gi * kcw, kw * 2,
+                                    (const char*)a->K + (size_t)b * a->bsk * 2 + gi * kcw, (size_t)a->ldk * 2, kcw, a->Lk,
+                                    cudaMemcpyHostToDevice, h->copy_in));
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dV + (size_t)b * a->Lk * kw * 2 + gi * kcw, kw * 2,
+                                    (const char*)a->V + (size_t)b * a->bsv * 2 + gi * kcw, (size_t)a->ldv * 2, kcw, a->Lk,
+                                    cudaMemcpyHostToDevice, h->copy_in));
+    }
+    if (gi == 0) {
+    // The small operands (tables, weights, lengths) go right after the first group of heads and through a pinned bounce buffer: a copy from
+    // pageable memory would block the calling thread until the copy engine reaches it - behind the large
+    // transfers - and nothing could be launched meanwhile.
+    {
+      const size_t tbytes = a->rope_mode != KREA_CUDA_ROPE_NONE ? (size_t)trows * 64 * 4 : 0;
+      const size_t need = 2 * tbytes + 1024 + (size_t)batch * 4;
+      if (h->bounce_bytes < need) {
+        CUDA_TRY(h, cudaStreamSynchronize(h->copy_in));
+        if (h->bounce) cudaFreeHost(h->bounce);
+        h->bounce = nullptr;
+        h->bounce_bytes = 0;
+        if (cudaMallocHost(&h->bounce, need) != cudaSuccess) {
+          cudaGetLastError();
+          return fail(h, KREA_CUDA_E_NOMEM, "joint_attention_host: cannot allocate %zu bytes of pinned memory", need);
+        }
+        h->bounce_bytes = need;
+      } else {
+        CUDA_TRY(h, cudaEventSynchronize(h->pipe_ev[17]));   // the previous call's copies out of the bounce buffer
+      }
+      char* bb = (char*)h->bounce;
+      if (tbytes) {
+        memcpy(bb, a->cos, tbytes);
+        memcpy(bb + tbytes, a->sin, tbytes);
+        CUDA_TRY(h, cudaMemcpyAsync(dT, bb, 2 * tbytes, cudaMemcpyHostToDevice, h->copy_in));
+      }
+      memcpy(bb + 2 * tbytes, a->wq, 512);
+      memcpy(bb + 2 * tbytes + 512, a->wk, 512);
+      CUDA_TRY(h, cudaMemcpyAsync(dW, bb + 2 * tbytes, 1024, cudaMemcpyHostToDevice, h->copy_in));
+      if (a->text_len) {
+        memcpy(bb + 2 * tbytes + 1024, a->text_len, (size_t)batch * 4);
+        CUDA_TRY(h, cudaMemcpyAsync(dL, bb + 2 * tbytes + 1024, (size_t)batch * 4, cudaMemcpyHostToDevice, h->copy_in));
+      }
+      CUDA_TRY(h, cudaEventRecord(h->pipe_ev[17], h->copy_in));
+    }
+    }
+    CUDA_TRY(h, cudaEventRecord(h->pipe_ev[gi], h->copy_in));
+    if (ttrace) cudaEventRecord(tev[1 + gi], h->copy_in);
   }
   float* dcos = (float*)dT;
   float* dsin = dcos + (size_t)trows * 64;
-  if (a->rope_mode != KREA_CUDA_ROPE_NONE) {
-    CUDA_TRY(h, cudaMemcpyAsync(dcos, a->cos, (size_t)trows * 64 * 4, cudaMemcpyHostToDevice, h->stream));
-    CUDA_TRY(h, cudaMemcpyAsync(dsin, a->sin, (size_t)trows * 64 * 4, cudaMemcpyHostToDevice, h->stream));
+  for (int gi = 0; gi < ngroups; gi++) {
+    CUDA_TRY(h, cudaStreamWaitEvent(h->stream, h->pipe_ev[gi], 0));
+    krea_cuda_joint_args d = *a;
+    d.Q = (char*)dQ + gi * qcw; d.K = (char*)dK + gi * kcw; d.V = (char*)dV + gi * kcw; d.O = (char*)dO + gi * qcw;
+    d.batch = batch;
+    d.heads = hq_g;
+    d.ldq = d.ldo = (int)qw; d.ldk = d.ldv = (int)kw;
+    d.bsq = d.bso = (int64_t)a->Lq * qw; d.bsk = d.bsv = (int64_t)a->Lk * kw;
+    d.wq = (const float*)dW; d.wk = (const float*)dW + 128;
+    d.cos = dcos; d.sin = dsin;
+    d.text_len = a->text_len ? (const int32_t*)dL : nullptr;
+    d.G = nullptr; d.ldg = 0; d.bsg = 0;
+    d.k_scratch = nullptr; d.k_scratch_bytes = 0;
+    if ((rc = krea_cuda_joint_attention(h, &d))) return rc;
+    CUDA_TRY(h, cudaEventRecord(h->pipe_ev[8 + gi], h->stream));
+    if (ttrace) cudaEventRecord(tev[10 + gi], h->stream);
+    CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->pipe_ev[8 + gi], 0));
+    for (int b = 0; b < batch; b++)
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)a->O + (size_t)b * a->bso * 2 + gi * qcw, (size_t)a->ldo * 2,
+                                    (const char*)dO + (size_t)b * a->Lq * qw * 2 + gi * qcw, qw * 2, qcw, a->Lq,
+                                    cudaMemcpyDeviceToHost, h->copy_out));
+    if (ttrace) cudaEventRecord(tev[20 + gi], h->copy_out);
   }
-  CUDA_TRY(h, cudaMemcpyAsync(dW, a->wq, 512, cudaMemcpyHostToDevice, h->stream));
-  CUDA_TRY(h, cudaMemcpyAsync((char*)dW + 512, a->wk, 512, cudaMemcpyHostToDevice, h->stream));
-  if (a->text_len) CUDA_TRY(h, cudaMemcpyAsync(dL, a->text_len, (size_t)batch * 4, cudaMemcpyHostToDevice, h->stream));
-  krea_cuda_joint_args d = *a;
-  d.Q = dQ; d.K = dK; d.V = dV; d.O = dO;
-  d.batch = batch;
-  d.ldq = d.ldo = (int)qw; d.ldk = d.ldv = (int)kw;
-  d.bsq = d.bso = (int64_t)a->Lq * qw; d.bsk = d.bsv = (int64_t)a->Lk * kw;
-  d.wq = (const float*)dW; d.wk = (const float*)dW + 128;
-  d.cos = dcos; d.sin = dsin;
-  d.text_len = a->text_len ? (const int32_t*)dL : nullptr;
-  d.G = nullptr; d.ldg = 0; d.bsg = 0;
-  d.k_scratch = nullptr; d.k_scratch_bytes = 0;
-  if ((rc = krea_cuda_joint_attention(h, &d))) return rc;
-  for (int b = 0; b < batch; b++)
-    CUDA_TRY(h, cudaMemcpy2DAsync((char*)a->O + (size_t)b * a->bso * 2, (size_t)a->ldo * 2, (const char*)dO + (size_t)b * a->Lq * qw * 2, qw * 2,
-                                  qw * 2, a->Lq, cudaMemcpyDeviceToHost, h->stream));
+  CUDA_TRY(h, cudaStreamSynchronize(h->copy_out));
+  if (ttrace) {
+    cudaDeviceSynchronize();
+    fprintf(stderr, "[krea_cuda host pipeline] groups=%d, ms since first copy:", ngroups);
+    for (int gi = 0; gi < ngroups; gi++) {
+      float t1 = 0, t2 = 0, t3 = 0;
+      cudaEventElapsedTime(&t1, tev[0], tev[1 + gi]);
+      cudaEventElapsedTime(&t2, tev[0], tev[10 + gi]);
+      cudaEventElapsedTime(&t3, tev[0], tev[20 + gi]);
+      fprintf(stderr, "  g%d in %.3f compute %.3f out %.3f;", gi, t1, t2, t3);
+    }
+    fprintf(stderr, "\n");
+    for (int i = 0; i < 32; i++) cudaEventDestroy(tev[i]);
+  }
   return krea_cuda_sync(h);
 }
 

@@ -148,6 +148,52 @@ def test_attention_operator_shapes(kc, Lq, Lk, H, group):
     assert np.all(got[:, H * 128:] == 7.0)     # columns past heads*128 are not touched
 
 
+@pytest.mark.parametrize("Lq,Lk,q_pos0,H,group", [(300, 300, 0, 2, 1), (200, 456, 256, 4, 2), (130, 700, 100, 2, 1), (64, 64, -10, 1, 1)])
+def test_attention_causal(kc, Lq, Lk, q_pos0, H, group):
+    """The text-encoder caller of Metal::attention (model.mm:151-157): causal after a cached prefix, key k visible
+    to row i iff k <= i + q_pos0 (attention.metal:237-249); rows that see no key give zeros."""
+    rng = np.random.default_rng(Lq + Lk)
+    kvh = H // group
+    Q = synth.f32_to_bf16_bits(rng.standard_normal((Lq, H * 128)).astype(np.float32))
+    K = synth.f32_to_bf16_bits(rng.standard_normal((Lk, kvh * 128)).astype(np.float32))
+    V = synth.f32_to_bf16_bits(rng.standard_normal((Lk, kvh * 128)).astype(np.float32))
+    want = oracle.attention(Q, K, V, Lq, Lk, H, H * 128, kvh * 128, kvh * 128, group=group, causal=True, q_pos0=q_pos0)
+    o = torch.full((Lq, H * 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, H * 128, kvh * 128, kvh * 128, H * 128, group, True, q_pos0)
+    kc.wait()
+    got = host_f32(o)
+    check(got, want, None, f"causal {Lq}x{Lk} q_pos0={q_pos0}")
+    if q_pos0 < 0:
+        assert np.all(got[:-q_pos0] == 0)
+
+
+def test_attention_big_dim_rank1_term(kc):
+    """Block 0 of the reference model: one head dimension is split off in fp32 by qk_norm_rope (big_dim) and
+    comes back as the rank-1 score term QB[q, h] * KB[k, h / group] (norm.metal:68-71, attention.metal:232-234)."""
+    rng = np.random.default_rng(47)
+    rows, H, group = 400, 4, 2
+    kvh = H // group
+    ld = (H + 2 * kvh) * 128
+    base = synth.f32_to_bf16_bits(rng.standard_normal((rows, ld)).astype(np.float32))
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wq[37] = wk[37] = 6.0                                       # a dominant dimension
+    cos, sin = synth.rope_tables_ref3axis(80, 16, 20)
+    ref = base.copy()
+    qb_w, kb_w = oracle.qk_norm_rope(ref, wq, wk, cos, sin, rows, ld, 0, H, H * 128, kvh, 1e-5, 0, big_dim=37)
+    flat = ref.reshape(-1)
+    want = oracle.attention(flat, flat[H * 128:], flat[(H + kvh) * 128:], rows, rows, H, ld, ld, ld, group=group, QB=qb_w, KB=kb_w)
+    x = dev_bits(base)
+    qb = torch.zeros(rows, H, device="cuda")
+    kb = torch.zeros(rows, kvh, device="cuda")
+    kc.qk_norm_rope(x, dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin), rows, ld, 0, H, H * 128, kvh, 1e-5, 0, 37, qb, kb)
+    xf = x.view(-1)
+    o = torch.zeros((rows, H * 128), dtype=torch.bfloat16, device="cuda")
+    kc.attention(xf, xf[H * 128:], xf[(H + kvh) * 128:], o, rows, rows, H, ld, ld, ld, H * 128, group, False, 0, None, 0, qb, kb)
+    kc.wait()
+    check(host_f32(o), want, None, "big-dim rank-1 term")
+
+
 def test_attention_gate(kc):
     rng = np.random.default_rng(41)
     Lq, Lk, H = 200, 300, 3
@@ -249,6 +295,28 @@ def test_joint_caller_scratch_and_host_entry(kc):
     assert np.array_equal(out.view(np.int16), o.view(torch.int16).cpu().numpy())    # same kernels, same bits
 
 
+def test_host_entry_pipelined_over_head_groups(kc):
+    """Above 8 MB of input the host-pointer call overlaps PCIe copies with compute, one group of heads at a
+    time; heads are independent, so the output must equal the single device call bit for bit."""
+    H, group, T, gh, gw = 8, 2, 512, 32, 48
+    S = T + gh * gw                                    # 2048 rows, 16.8 MB of q|k|v
+    qkv, wq, wk, cos, sin = rand_case(63, 1, S, H, T, gh, gw, group)
+    kvh = H // group
+    ld = (H + 2 * kvh) * 128
+    tl = np.array([300], dtype=np.int32)
+    want = oracle.joint_attention(qkv, 1, S, H, wq, wk, cos, sin, text_len=tl, text_slots=T, group=group)
+    got_dev = run_joint(kc, qkv, 1, S, H, wq, wk, cos, sin, group=group, text_len=tl, text_slots=T)
+    n0 = kc.launches
+    out = np.zeros((1, S, H * 128), dtype=np.uint16)
+    flat = qkv.reshape(-1)
+    kc.joint_attention_host(flat, flat[H * 128:], flat[(H + kvh) * 128:], out, S, S, H, ld, ld, ld, H * 128, wq, wk, cos, sin,
+                            1e-6, group, batch=1, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=tl, text_slots=T)
+    assert kc.launches - n0 == 2 * 4                   # four head groups, pre-pass + attention each
+    got = synth.bf16_bits_to_f32(out)
+    check(got, want, None, "pipelined host entry")
+    assert np.array_equal(got, got_dev)
+
+
 def test_argument_errors_launch_nothing(kc):
     n0 = kc.launches
     t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")
@@ -267,8 +335,9 @@ def test_argument_errors_launch_nothing(kc):
     with pytest.raises(ops.KreaCudaError) as e:
         kc.attention(t.view(-1)[1:], t, t, t, 16, 16, 1, 128, 128, 128, 128)   # misaligned pointer
     assert e.value.code == binding.E_ARG
-    with pytest.raises(ops.KreaCudaError) as e:
-        kc.attention(t, t, t, t, 16, 16, 1, 128, 128, 128, 128, 1, True, 0)    # causal: not built, never silently wrong
+    with pytest.raises(ops.KreaCudaError) as e:                                # a combination that is not built is
+        kc.attention(t, t, t, t, 16, 16, 1, 128, 128, 128, 128, 1, True, 0,    # refused, never silently wrong
+                     text_len=torch.zeros(1, dtype=torch.int32, device="cuda"), text_slots=8)
     assert e.value.code == binding.E_UNSUPPORTED
     with pytest.raises(ops.KreaCudaError) as e:
         kc.qk_norm_rope(t, f, f, f, f, 4, 128, 0, 1, 0, 0, 1e-6, 0, 5, None, None)   # big_dim without buffers (metal.mm:185)

@@ -13,10 +13,9 @@
 
 namespace krea {
 
-// One warp per row (grid-stride over batch x rows), looping over the row's heads two at a time: 16 lanes
-// cover one head with 16 bytes (8 channels) each, so a warp load is 512 contiguous bytes.  The row's
-// cos/sin entries and the weights depend only on the lane's channels, not on the head, and stay in
-// registers across the head loop.
+// One warp per (row, eight heads) unit, two heads per step: 16 lanes cover one head with 16 bytes (8
+// channels) each, so a warp load is 512 contiguous bytes.  The row's cos/sin entries and the weights depend
+// only on the lane's channels, not on the head, and are loaded once per unit.
 __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams p) {
   const int lane = threadIdx.x & 31;
   if (p.bound_wq != nullptr && blockIdx.x == 0 && threadIdx.x < 32) {
@@ -46,9 +45,13 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
     const float4 a = __ldg((const float4*)p.wk + 2 * c), bk = __ldg((const float4*)p.wk + 2 * c + 1);
     wkv[0] = a.x; wkv[1] = a.y; wkv[2] = a.z; wkv[3] = a.w; wkv[4] = bk.x; wkv[5] = bk.y; wkv[6] = bk.z; wkv[7] = bk.w;
   }
-  const int nrows = p.batch * p.rows;
-  const int wstride = gridDim.x * (blockDim.x >> 5);
-  for (int rb = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); rb < nrows; rb += wstride) {
+  // work unit = (row, batch of up to eight heads): short dependent chains (weights, tables, one batch of
+  // loads) and enough warps in flight to cover the memory latency even for a few thousand rows
+  const int nhb = (heads + 7) >> 3;
+  const long long nunits = (long long)p.batch * p.rows * nhb;
+  const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nunits; u += wstride) {
+    const int rb = (int)(u / nhb), hb = (int)(u - (long long)rb * nhb) * 8;
     const int b = rb / p.rows, row = rb - b * p.rows;
     const __nv_bfloat16* srow = p.src + (size_t)b * p.bs_src + (size_t)row * p.ld_src;
     __nv_bfloat16* drow = p.dst + (size_t)b * p.bs_dst + (size_t)row * p.ld_dst;
@@ -67,8 +70,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
       cf[0] = c0.x; cf[1] = c0.y; cf[2] = c0.z; cf[3] = c0.w; cf[4] = c1.x; cf[5] = c1.y; cf[6] = c1.z; cf[7] = c1.w;
       sf[0] = s0.x; sf[1] = s0.y; sf[2] = s0.z; sf[3] = s0.w; sf[4] = s1.x; sf[5] = s1.y; sf[6] = s1.z; sf[7] = s1.w;
     }
-    // four steps (eight heads) per batch: their loads are all issued before the first one is used
-    for (int hb = 0; hb < heads; hb += 8) {
+    // four steps (eight heads): their loads are all issued before the first one is used
+    {
       uint4 raw[4];
       int dcol[4], hl[4];
       bool live[4], isq[4];
@@ -139,7 +142,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
 cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
   const long long nrows = (long long)p.batch * p.rows;
   if (nrows <= 0 || p.n_q + p.n_k <= 0) return cudaSuccess;
-  long long blocks = (nrows + 7) / 8;    // 8 warps per CTA, one row per warp and step
+  const long long nunits = nrows * ((p.n_q + p.n_k + 7) / 8);
+  long long blocks = (nunits + 7) / 8;   // 8 warps per CTA, one (row, eight heads) unit per warp and step
   const long long cap = 148LL * 8;       // all resident at once; the loop strides over the rest
   if (blocks > cap) blocks = cap;
   qk_norm_rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);

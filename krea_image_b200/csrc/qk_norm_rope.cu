@@ -16,7 +16,10 @@ namespace krea {
 // One warp per (row, eight heads) unit, two heads per step: 16 lanes cover one head with 16 bytes (8
 // channels) each, so a warp load is 512 contiguous bytes.  The row's cos/sin entries and the weights depend
 // only on the lane's channels, not on the head, and are loaded once per unit.
-__global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams p) {
+// MODE is the rope mode as a compile-time constant (dead branches cost registers, and registers decide
+// how many warps cover the memory latency).
+template <int MODE>
+__global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopeParams p) {
   const int lane = threadIdx.x & 31;
   if (p.bound_wq != nullptr && blockIdx.x == 0 && threadIdx.x < 32) {
     // After RMSNorm every head vector has norm <= sqrt(128) * max|w| (RoPE is a rotation), so
@@ -57,12 +60,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
     __nv_bfloat16* drow = p.dst + (size_t)b * p.bs_dst + (size_t)row * p.ld_dst;
     const size_t trow = (size_t)(p.row0 + row) * 64;
     float cf[8], sf[8];
-    if (p.rope_mode == 0) {
+    if (MODE == 0) {
       // interleaved pairs (2i, 2i+1) share frequency i: this chunk holds pairs 4c .. 4c+3
       const float4 cc = __ldg((const float4*)(p.cos + trow) + c), sc = __ldg((const float4*)(p.sin + trow) + c);
       cf[0] = cc.x; cf[1] = cc.y; cf[2] = cc.z; cf[3] = cc.w;
       sf[0] = sc.x; sf[1] = sc.y; sf[2] = sc.z; sf[3] = sc.w;
-    } else if (p.rope_mode == 1) {
+    } else if (MODE == 1) {
       // rotate-half: channel i pairs with i + 64 (the lane 8 chunks away); both use frequency i mod 64
       const int f = (c & 7) * 2;
       const float4 c0 = __ldg((const float4*)(p.cos + trow) + f), c1 = __ldg((const float4*)(p.cos + trow) + f + 1);
@@ -104,13 +107,13 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kernel(const NormRopeParams 
         const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
 #pragma unroll
         for (int e = 0; e < 8; e++) y[e] *= rrms * (isq[i] ? wqv[e] : wkv[e]);
-        if (p.rope_mode == 0) {
+        if (MODE == 0) {
 #pragma unroll
           for (int e = 0; e < 4; e++) {
             z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
             z[2 * e + 1] = y[2 * e] * sf[e] + y[2 * e + 1] * cf[e];
           }
-        } else if (p.rope_mode == 1) {
+        } else if (MODE == 1) {
           const float sg = c < 8 ? -1.f : 1.f;
 #pragma unroll
           for (int e = 0; e < 8; e++) {
@@ -144,9 +147,11 @@ cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
   if (nrows <= 0 || p.n_q + p.n_k <= 0) return cudaSuccess;
   const long long nunits = nrows * ((p.n_q + p.n_k + 7) / 8);
   long long blocks = (nunits + 7) / 8;   // 8 warps per CTA, one (row, eight heads) unit per warp and step
-  const long long cap = 148LL * 8;       // all resident at once; the loop strides over the rest
+  const long long cap = 148LL * 3;       // all resident at once; the loop strides over the rest
   if (blocks > cap) blocks = cap;
-  qk_norm_rope_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
+  if (p.rope_mode == 0) qk_norm_rope_kernel<0><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else if (p.rope_mode == 1) qk_norm_rope_kernel<1><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  else qk_norm_rope_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -25,24 +25,42 @@ def _mix(z: np.ndarray) -> np.ndarray:
     return z ^ (z >> np.uint64(31))
 
 
+def _normal_pairs(seed: int, even: np.ndarray):
+    """Box-Muller pairs driven by counters (even, even+1): the cos and the sin branch as float64."""
+    with np.errstate(over="ignore"):
+        base = np.uint64(seed) * _GOLD
+        a = _mix(base + even)
+        b = _mix(base + even + np.uint64(1))
+    u1 = ((a >> np.uint64(11)).astype(np.float64) + 1.0) / 9007199254740993.0
+    u2 = (b >> np.uint64(11)).astype(np.float64) / 9007199254740992.0
+    r = np.sqrt(-2.0 * np.log(u1))
+    t = 2.0 * np.pi * u2
+    return r * np.cos(t), r * np.sin(t)
+
+
 def normal_f32(seed: int, first: int, n: int) -> np.ndarray:
     """Elements [first, first+n) of stream `seed` as float32.  Elements (2i, 2i+1) are the cos and sin
     branch of one Box-Muller pair driven by counters 2i and 2i+1."""
     lo = first & ~1
     hi = (first + n + 1) & ~1
-    with np.errstate(over="ignore"):
-        i = np.arange(lo, hi, 2, dtype=np.uint64)
-        base = np.uint64(seed) * _GOLD
-        a = _mix(base + i)
-        b = _mix(base + i + np.uint64(1))
-    u1 = ((a >> np.uint64(11)).astype(np.float64) + 1.0) / 9007199254740993.0
-    u2 = (b >> np.uint64(11)).astype(np.float64) / 9007199254740992.0
-    r = np.sqrt(-2.0 * np.log(u1))
-    t = 2.0 * np.pi * u2
+    c, sn = _normal_pairs(seed, np.arange(lo, hi, 2, dtype=np.uint64))
     out = np.empty(hi - lo, dtype=np.float32)
-    out[0::2] = r * np.cos(t)
-    out[1::2] = r * np.sin(t)
+    out[0::2] = c
+    out[1::2] = sn
     return out[first - lo:first - lo + n]
+
+
+def normal_f32_rows(seed: int, first: int, row_stride: int, nrows: int, width: int) -> np.ndarray:
+    """float32 [nrows, width]: row r holds elements [first + r*row_stride, +width) of the stream
+    (first, row_stride and width even, so no Box-Muller pair straddles a row)."""
+    assert first % 2 == 0 and row_stride % 2 == 0 and width % 2 == 0
+    even = (np.uint64(first) + np.arange(nrows, dtype=np.uint64)[:, None] * np.uint64(row_stride)
+            + np.arange(0, width, 2, dtype=np.uint64)[None, :])
+    c, sn = _normal_pairs(seed, even)
+    out = np.empty((nrows, width), dtype=np.float32)
+    out[:, 0::2] = c
+    out[:, 1::2] = sn
+    return out
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
@@ -169,9 +187,10 @@ def qkv_slice(cfg: Config, head0: int = 0, nheads: int = None, row0: int = 0, nr
                 first = ((t * B + b0 + b) * S + row0) * H * HEAD_DIM
                 out[b, :, t, :] = normal_bf16(cfg.seed, first, nrows * width).reshape(nrows, width)
             else:
-                for s in range(nrows):
-                    first = ((t * B + b0 + b) * S + row0 + s) * H * HEAD_DIM + head0 * HEAD_DIM
-                    out[b, s, t, :] = f32_to_bf16_bits(normal_f32(cfg.seed, first, width))
+                for s0 in range(0, nrows, 8192):
+                    m = min(8192, nrows - s0)
+                    first = ((t * B + b0 + b) * S + row0 + s0) * H * HEAD_DIM + head0 * HEAD_DIM
+                    out[b, s0:s0 + m, t, :] = f32_to_bf16_bits(normal_f32_rows(cfg.seed, first, H * HEAD_DIM, m, width))
     return out.reshape(nb, nrows, 3 * width)
 
 

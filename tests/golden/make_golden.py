@@ -55,10 +55,39 @@ def case_config(cid: int, heads_sel, rows_per_head: int):
     return out
 
 
+def case_big(cid: int, heads_sel, rows_per_head: int):
+    """Sampled rows of a long-sequence configuration, computed from one-head slices of the inputs (the
+    counter-based generator gives any slice), so the fixture and its CPU check never hold the full tensors."""
+    cfg = synth.CONFIGS[cid]
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    rng = np.random.default_rng(1000 + cid)
+    out = {"cid": cid, "wq_crc": crc(wq), "wk_crc": crc(wk), "cos_crc": crc(cos), "sin_crc": crc(sin)}
+    rows_all, f32_all, ref_all, crcs = [], [], [], []
+    for h in heads_sel:
+        q1 = synth.qkv_slice(cfg, head0=h, nheads=1)[0]          # [S, 3*128]: a one-head model with the same numbers
+        rows = np.sort(rng.choice(cfg.seq, size=rows_per_head, replace=False)).astype(np.int32)
+        rows[0], rows[1], rows[-2], rows[-1] = 0, cfg.text - 1, cfg.text, cfg.seq - 1
+        rows = np.sort(rows)
+        f32_all.append(oracle.joint_attention_rows(q1, cfg.seq, 1, 0, wq, wk, cos, sin, rows))
+        ref_all.append(oracle.joint_attention_rows(q1, cfg.seq, 1, 0, wq, wk, cos, sin, rows, ref_rounding=True))
+        rows_all.append(rows)
+        crcs.append(crc(q1))
+    out["rows"] = np.stack(rows_all)
+    out["sample"] = np.zeros(len(heads_sel), dtype=np.int32)
+    out["head_of_block"] = np.array(heads_sel, dtype=np.int32)
+    out["head_slice_crc"] = np.array(crcs, dtype=np.int64)
+    out["fp32"] = np.stack(f32_all)
+    out["ref"] = np.stack(ref_all)
+    return out
+
+
 def main():
     np.savez_compressed(os.path.join(HERE, "c0_rows.npz"), **case_config(0, [0, 7, 23], 24))
     np.savez_compressed(os.path.join(HERE, "c1_rows.npz"), **case_config(1, [0, 11, 23], 16))
     np.savez_compressed(os.path.join(HERE, "c2_rows.npz"), **case_config(2, [3, 20], 12))
+    np.savez_compressed(os.path.join(HERE, "c3_rows.npz"), **case_big(3, [2, 9, 17, 23], 16))
+    np.savez_compressed(os.path.join(HERE, "c4_rows.npz"), **case_big(4, [1, 12, 22], 12))
     # generator known answers: first values of a few streams
     ka = {f"normal_seed{sd}_first{fi}": oracle.gen_normal_bf16(sd, fi, 16) for sd, fi in ((1234, 0), (1235, 7), (1238, 1 << 33))}
     ka["uniform_1234"] = oracle.gen_uniform_f32(1234, 3 << 40, 0.5, 1.5, 8)

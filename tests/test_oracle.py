@@ -240,6 +240,29 @@ def test_golden_fixture_inputs_and_outputs(name):
         assert zlib.crc32(qkv_b.tobytes()) == int(g["qkv_crc"])
 
 
+@pytest.mark.parametrize("name", ["c3_rows", "c4_rows"])
+def test_golden_fixture_long_sequences(name):
+    """Fixtures of the long-sequence configurations, recomputed from a one-head slice of the inputs."""
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    cfg = synth.CONFIGS[int(g["cid"])]
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    assert zlib.crc32(wq.tobytes()) == int(g["wq_crc"]) and zlib.crc32(cos.tobytes()) == int(g["cos_crc"])
+    h, rows = int(g["head_of_block"][0]), g["rows"][0]
+    q1 = synth.qkv_slice(cfg, head0=h, nheads=1)[0]
+    assert zlib.crc32(q1.tobytes()) == int(g["head_slice_crc"][0])
+    got = oracle.joint_attention_rows(q1, cfg.seq, 1, 0, wq, wk, cos, sin, rows)
+    assert np.allclose(got, g["fp32"][0], atol=1e-6)
+    assert rows[0] == 0 and rows[-1] == cfg.seq - 1 and cfg.text - 1 in rows and cfg.text in rows
+
+
+def test_head_slices_equal_columns_of_the_full_tensor():
+    cfg = synth.CONFIGS[0]
+    full = synth.qkv_slice(cfg).reshape(1, cfg.seq, 3, cfg.heads, 128)
+    part = synth.qkv_slice(cfg, head0=3, nheads=2, row0=5, nrows=100)
+    assert np.array_equal(full[:, 5:105, :, 3:5].reshape(1, 100, -1), part)
+
+
 def test_flop_count():
     assert synth.attention_flops(synth.CONFIGS[1]) == pytest.approx(2.6092e11, rel=1e-4)
     assert synth.attention_flops(synth.CONFIGS[0]) == pytest.approx(2.899e10, rel=1e-3)

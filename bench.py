@@ -167,7 +167,11 @@ def run_seq_parallel(args, rank, world, local_rank):
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     d_wq, d_wk, d_cos, d_sin = dev(wq), dev(wk), dev(cos), dev(sin)
     flops = synth.attention_flops(cfg)
-    if world > 1:
+    if world > 1 and args.a2a == "native":
+        kd.init_native(kc)                     # the library's own NCCL communicator: one C call per step
+        ua = kd.NativeUlyssesAttention(kc, plan)
+        step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
+    elif world > 1:
         ua = kd.UlyssesAttention(kc, plan, kd.TorchGroup())
         step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
     else:
@@ -212,6 +216,7 @@ def run_seq_parallel(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "batch": 1, "heads": H, "seq": S, "head_dim": 128,
                        "parallelism": f"sequence-sharded in/out, all-to-all to {H // world} heads per GPU" if world > 1 else "single GPU",
+                       "exchange": ("ncclSend/ncclRecv inside libkrea_cuda" if args.a2a == "native" else "torch.distributed all_to_all_single") if world > 1 else None,
                        "l2": "inputs (1.2 GB) exceed the 126 MB L2"},
             "pct_of_measured_bf16_peak": 100.0 * value / world / peak, "gpu_launches": int(launches), "clocks": clocks,
             "e2e": None, "roofline": None}))
@@ -363,6 +368,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--a2a", default="native", choices=["native", "torch"],
+                    help="workload c4 on several GPUs: who carries the all-to-all (the library's NCCL communicator, or torch.distributed)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

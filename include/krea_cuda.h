@@ -44,7 +44,9 @@ enum {
   KREA_CUDA_E_UNSUPPORTED = -2, /* valid in the reference's API but not built here; nothing was launched */
   KREA_CUDA_E_CUDA = -3,        /* a CUDA runtime / driver call failed */
   KREA_CUDA_E_DEVICE = -4,      /* a kernel gave up on a bounded wait and reported it (see krea_cuda_sync) */
-  KREA_CUDA_E_NOMEM = -5        /* workspace allocation failed or caller-provided scratch too small */
+  KREA_CUDA_E_NOMEM = -5,       /* workspace allocation failed or caller-provided scratch too small */
+  KREA_CUDA_E_COMM = -6,        /* NCCL could not be loaded, or a communicator call failed */
+  KREA_CUDA_E_TIMEOUT = -7      /* krea_cuda_dist_sync gave up waiting and aborted the communicator */
 };
 
 /* RoPE modes of qk_norm_rope: enum RopeMode, engine/src/metal.h:44; engine/kernels/norm.metal:64-66. */
@@ -214,6 +216,61 @@ typedef struct {
 } krea_cuda_reshard_args;
 KREA_CUDA_API int krea_cuda_reshard_pack(krea_cuda* h, const krea_cuda_reshard_args* a);
 KREA_CUDA_API int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a);
+
+/* ---- sequence-parallel execution over NCCL (no counterpart in the reference, which is single-device) ----
+ * One process and one handle per GPU.  The library loads NCCL at run time (dlopen of "libnccl.so.2", or of
+ * the path in the environment variable KREA_CUDA_NCCL_LIB), so nothing here is needed to use the
+ * single-GPU entry points.  Rank 0 obtains an id with krea_cuda_dist_unique_id and hands the 128 bytes to
+ * every rank by whatever means the host program has (a file, a socket, MPI, torch.distributed);
+ * krea_cuda_dist_init is collective over the nranks handles.  Everything is enqueued on the handle's
+ * stream; remote rows are always landed in local memory by NCCL before a kernel of this library reads
+ * them.
+ *
+ * Layout: with S rows and H heads over P ranks (S and H multiples of P), rank r starts with rows
+ * [r*S/P, (r+1)*S/P) of every head ("sequence-sharded") and the exchange gives it every row of heads
+ * [r*H/P, (r+1)*H/P) ("head-sharded"), where the single-GPU kernel runs unchanged - the RoPE position
+ * of a row depends only on its global index, so the prologue runs after the exchange with the global
+ * tables. */
+#define KREA_CUDA_DIST_ID_BYTES 128
+KREA_CUDA_API int krea_cuda_dist_unique_id(void* id_out /* KREA_CUDA_DIST_ID_BYTES */, char* err, int errlen);
+KREA_CUDA_API int krea_cuda_dist_init(krea_cuda* h, int rank, int nranks, const void* id);
+KREA_CUDA_API int krea_cuda_dist_rank(krea_cuda* h);    /* -1 before krea_cuda_dist_init */
+KREA_CUDA_API int krea_cuda_dist_size(krea_cuda* h);    /* 0 before krea_cuda_dist_init */
+/* Waits for the handle's stream for at most timeout_ms (<= 0: no limit), polling the communicator for
+ * asynchronous errors.  On an error or a timeout the communicator is aborted, so that no collective is
+ * left waiting for a peer that will not come, and KREA_CUDA_E_COMM / KREA_CUDA_E_TIMEOUT is returned;
+ * the handle then accepts single-GPU calls only, until krea_cuda_dist_init is called again. */
+KREA_CUDA_API int krea_cuda_dist_sync(krea_cuda* h, int timeout_ms);
+KREA_CUDA_API int krea_cuda_dist_shutdown(krea_cuda* h); /* collective; also done by krea_cuda_destroy */
+
+typedef struct {
+  const void* src;   /* seq_to_heads: local rows [rows_local][src_ld]; heads_to_seq: [nranks*rows_local][cols_per_rank] */
+  void* dst;         /* seq_to_heads: [nranks*rows_local][cols_per_rank] contiguous; heads_to_seq: local rows [rows_local][dst_ld] */
+  int rows_local;    /* S / nranks */
+  int cols_per_rank; /* (H / nranks) * 128 */
+  int src_ld, dst_ld;     /* leading dimension of the sequence-sharded side (the other side is contiguous) */
+  int src_col0, dst_col0; /* first column of the head block on the sequence-sharded side */
+} krea_cuda_a2a_args;
+/* dst[p*rows_local + i][c] = (rank p's src)[i][src_col0 + rank*cols_per_rank + c] */
+KREA_CUDA_API int krea_cuda_reshard_seq_to_heads(krea_cuda* h, const krea_cuda_a2a_args* a);
+/* dst[i][dst_col0 + p*cols_per_rank + c] = (rank p's src)[rank*rows_local + i][c] */
+KREA_CUDA_API int krea_cuda_reshard_heads_to_seq(krea_cuda* h, const krea_cuda_a2a_args* a);
+
+/* The fused call on sequence-sharded rows: three exchanges (K first, so that its normalisation pass
+ * overlaps the exchange of V and Q on a second stream), the joint attention on the local heads, and
+ * the exchange of the output back.  Q, K, V: local rows [rows_local][ld*] holding all `heads` (K, V:
+ * heads/group) heads; O: local rows [rows_local][ldo], all heads.  cos/sin: the global tables
+ * [seq][64].  batch, the padding mask and the gate are not supported here.  Workspace (about six
+ * times seq * heads/nranks * 256 bytes) is owned by the handle and grown on demand. */
+typedef struct {
+  const void* Q; const void* K; const void* V; void* O;
+  int seq, heads, group;
+  int ldq, ldk, ldv, ldo;
+  const float* wq; const float* wk; const float* cos; const float* sin;
+  float eps;
+  int rope_mode;
+} krea_cuda_seqpar_args;
+KREA_CUDA_API int krea_cuda_seqpar_joint_attention(krea_cuda* h, const krea_cuda_seqpar_args* a);
 
 #ifdef __cplusplus
 }

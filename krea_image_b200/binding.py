@@ -9,9 +9,10 @@ import os
 
 from . import build as _build
 
-OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM = 0, -1, -2, -3, -4, -5
+OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM, E_COMM, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
 STATIC_SCRATCH_BYTES = 32 << 20   # KREA_CUDA_STATIC_SCRATCH_BYTES
+DIST_ID_BYTES = 128                # KREA_CUDA_DIST_ID_BYTES
 
 _vp = ctypes.c_void_p
 _int = ctypes.c_int
@@ -49,6 +50,18 @@ class ReshardArgs(ctypes.Structure):
                 ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
 
 
+class A2AArgs(ctypes.Structure):
+    _fields_ = [("src", _vp), ("dst", _vp), ("rows_local", _int), ("cols_per_rank", _int),
+                ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
+
+
+class SeqParArgs(ctypes.Structure):
+    _fields_ = [("Q", _vp), ("K", _vp), ("V", _vp), ("O", _vp),
+                ("seq", _int), ("heads", _int), ("group", _int),
+                ("ldq", _int), ("ldk", _int), ("ldv", _int), ("ldo", _int),
+                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("eps", ctypes.c_float), ("rope_mode", _int)]
+
+
 # every symbol include/krea_cuda.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "krea_cuda_create": (_vp, [_int, ctypes.c_char_p, _int]),
@@ -69,6 +82,15 @@ SYMBOLS = {
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
     "krea_cuda_reshard_pack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_reshard_unpack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
+    "krea_cuda_dist_unique_id": (_int, [_vp, ctypes.c_char_p, _int]),
+    "krea_cuda_dist_init": (_int, [_vp, _int, _int, _vp]),
+    "krea_cuda_dist_rank": (_int, [_vp]),
+    "krea_cuda_dist_size": (_int, [_vp]),
+    "krea_cuda_dist_sync": (_int, [_vp, _int]),
+    "krea_cuda_dist_shutdown": (_int, [_vp]),
+    "krea_cuda_reshard_seq_to_heads": (_int, [_vp, ctypes.POINTER(A2AArgs)]),
+    "krea_cuda_reshard_heads_to_seq": (_int, [_vp, ctypes.POINTER(A2AArgs)]),
+    "krea_cuda_seqpar_joint_attention": (_int, [_vp, ctypes.POINTER(SeqParArgs)]),
 }
 
 _lib = None

@@ -14,8 +14,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT_DIR, "libkrea_cuda.so")
-SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "qk_norm_rope.cu"]
-HEADERS = ["attention_sm100.h", "sm100_ptx.cuh", os.path.join("..", "..", "include", "krea_cuda.h")]
+SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "qk_norm_rope.cu", "dist_nccl.cu"]
+HEADERS = ["attention_sm100.h", "sm100_ptx.cuh", "handle.h", os.path.join("..", "..", "include", "krea_cuda.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
 
@@ -67,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if pr.returncode:
             raise RuntimeError(f"nvcc failed on {src}")
         _check_register_budget(out)
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs, "-cudart", "static"]
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs, "-cudart", "static", "-ldl"]
     subprocess.run(cmd, check=True)
     return LIB
 

@@ -1,0 +1,71 @@
+// Private to the library: the handle behind `krea_cuda*` and the error helpers shared by its source files.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/krea_cuda.h"
+
+struct KreaDist;   // NCCL state of the sequence-parallel entry points (dist_nccl.cu)
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct krea_cuda {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  uint32_t* status_dev = nullptr;   // kernels report timed-out waits here
+  uint32_t* status_host = nullptr;  // pinned mirror
+  void* ws = nullptr;               // scratch for the normalised K of the joint call
+  size_t ws_bytes = 0;
+  void* stage[8] = {};              // device copies for the host-pointer entry point
+  size_t stage_bytes[8] = {};
+  uint64_t launches = 0;
+  PFN_encodeTiled encode = nullptr;
+  int split = 1;                    // softmax threads per query row
+  int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
+  bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host entry point: H2D and D2H streams
+  cudaEvent_t pipe_ev[18] = {};                   // [0,8) group in, [8,16) group out, 16 start, 17 bounce
+  void* bounce = nullptr;           // pinned host staging for the small operands of the host entry point
+  size_t bounce_bytes = 0;
+  bool profiling = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
+  std::vector<cudaEvent_t> event_pool;
+  KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
+};
+
+static inline int fail(krea_cuda* h, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (h) h->err = buf;
+  return code;
+}
+#define CUDA_TRY(h, expr)                                                                       \
+  do {                                                                                          \
+    cudaError_t e_ = (expr);                                                                    \
+    if (e_ != cudaSuccess) return fail(h, KREA_CUDA_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+
+// Implemented in krea_cuda.cu for the other source files of the library.
+// the fused call in two steps: K normalisation pass (+ logit bound), then the attention kernel
+int krea_joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch);
+int krea_joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch);
+int krea_validate_joint(krea_cuda* h, const krea_cuda_joint_args* a);
+// Implemented in dist_nccl.cu: releases the communicator and its workspace (called by krea_cuda_destroy).
+void krea_dist_release(krea_cuda* h);

@@ -17,37 +17,9 @@
 
 #include "../../include/krea_cuda.h"
 #include "attention_sm100.h"
+#include "handle.h"
 
 using namespace krea;
-
-typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-struct krea_cuda {
-  int device = 0;
-  cudaStream_t own_stream = nullptr;
-  cudaStream_t stream = nullptr;
-  std::string err;
-  uint32_t* status_dev = nullptr;   // kernels report timed-out waits here
-  uint32_t* status_host = nullptr;  // pinned mirror
-  void* ws = nullptr;               // scratch for the normalised K of the joint call
-  size_t ws_bytes = 0;
-  void* stage[8] = {};              // device copies for the host-pointer entry point
-  size_t stage_bytes[8] = {};
-  uint64_t launches = 0;
-  PFN_encodeTiled encode = nullptr;
-  int split = 1;                    // softmax threads per query row
-  int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
-  bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
-  cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host entry point: H2D and D2H streams
-  cudaEvent_t pipe_ev[18] = {};                   // [0,8) group in, [8,16) group out, 16 start, 17 bounce
-  void* bounce = nullptr;           // pinned host staging for the small operands of the host entry point
-  size_t bounce_bytes = 0;
-  bool profiling = false;
-  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
-  std::vector<cudaEvent_t> event_pool;
-};
 
 // Brackets one kernel launch with events while profiling is on (kind 0 = prologue, 1 = attention).
 struct ProfileMark {
@@ -76,23 +48,6 @@ struct ProfileMark {
     h->marks[kind].push_back({e0, e1});
   }
 };
-
-static int fail(krea_cuda* h, int code, const char* fmt, ...) {
-  char buf[512];
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(buf, sizeof(buf), fmt, ap);
-  va_end(ap);
-  if (h) h->err = buf;
-  return code;
-}
-#define CUDA_TRY(h, expr)                                                                       \
-  do {                                                                                          \
-    cudaError_t e_ = (expr);                                                                    \
-    if (e_ != cudaSuccess) return fail(h, KREA_CUDA_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
-  } while (0)
-
-static bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
 extern "C" {
 
@@ -154,6 +109,7 @@ void krea_cuda_destroy(krea_cuda* h) {
   if (!h) return;
   cudaSetDevice(h->device);
   if (h->own_stream) cudaStreamSynchronize(h->own_stream);
+  krea_dist_release(h);
   if (h->status_dev) cudaFree(h->status_dev);
   if (h->status_host) cudaFreeHost(h->status_host);
   if (h->ws) cudaFree(h->ws);
@@ -387,7 +343,9 @@ size_t krea_cuda_joint_scratch_bytes(const krea_cuda_joint_args* a) {
   return batch * (size_t)a->Lk * (size_t)(a->heads / a->group) * 128 * 2;
 }
 
-static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+// The fused call in two steps, so that a caller inside the library can put other work between them:
+// joint_prepass writes the normalised + rotated K and the logit bound, joint_attend runs the attention kernel.
+static int joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
   const int batch = a->batch <= 0 ? 1 : a->batch;
   const int kvheads = a->heads / a->group;
   // K pre-pass: normalised + rotated K, written once to scratch [batch, Lk, kvheads*128]
@@ -420,17 +378,27 @@ static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* ks
     CUDA_TRY(h, launch_qk_norm_rope(n, h->stream));
   }
   h->launches++;
+  return KREA_CUDA_OK;
+}
 
+static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+  const int batch = a->batch <= 0 ? 1 : a->batch;
+  const int kvheads = a->heads / a->group;
   AttnCall c{};
   c.Q = a->Q; c.K = kscr; c.V = a->V; c.O = a->O;
   c.G = (a->G && a->ldg > 0) ? a->G : nullptr;
   c.batch = batch; c.Lq = a->Lq; c.Lk = a->Lk; c.heads = a->heads; c.group = a->group;
-  c.ldq = a->ldq; c.ldk = n.ld_dst; c.ldv = a->ldv; c.ldo = a->ldo; c.ldg = c.G ? a->ldg : 0;
-  c.bsq = a->bsq; c.bsk = n.bs_dst; c.bsv = a->bsv; c.bso = a->bso; c.bsg = c.G ? a->bsg : 0;
+  c.ldq = a->ldq; c.ldk = (int64_t)kvheads * 128; c.ldv = a->ldv; c.ldo = a->ldo; c.ldg = c.G ? a->ldg : 0;
+  c.bsq = a->bsq; c.bsk = (int64_t)a->Lk * kvheads * 128; c.bsv = a->bsv; c.bso = a->bso; c.bsg = c.G ? a->bsg : 0;
   c.wq = a->wq; c.cos = a->cos; c.sin = a->sin; c.eps = a->eps; c.rope_mode = a->rope_mode; c.q_row0 = a->q_row0;
   c.text_len = a->text_len; c.text_slots = a->text_slots;
-  c.logit_bound = n.bound_out;
+  c.logit_bound = (float*)(h->status_dev + 8);
   return run_attention(h, c);
+}
+
+static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+  const int rc = joint_prepass(h, a, kscr);
+  return rc ? rc : joint_attend(h, a, kscr);
 }
 
 static int validate_joint(krea_cuda* h, const krea_cuda_joint_args* a) {
@@ -757,3 +725,7 @@ int krea_cuda_reshard_pack(krea_cuda* h, const krea_cuda_reshard_args* a) { retu
 int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a) { return reshard(h, a, true); }
 
 }  // extern "C"
+
+int krea_joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch) { return joint_prepass(h, a, k_scratch); }
+int krea_joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch) { return joint_attend(h, a, k_scratch); }
+int krea_validate_joint(krea_cuda* h, const krea_cuda_joint_args* a) { return validate_joint(h, a); }

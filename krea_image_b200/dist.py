@@ -136,3 +136,43 @@ class UlyssesAttention:
         kc.joint_attention(q, k, v, o, plan.seq, plan.seq, plan.heads_local, cl, cl, cl, cl, wq, wk, cos, sin, eps,
                            1, rope_mode)
         return heads_to_seq(plan, self.comm, o, kc.reshard_unpack, self._alloc("r"))
+
+
+def init_native(kc, group=None):
+    """Creates the library's own NCCL communicator over the ranks of a torch.distributed group: rank 0
+    makes the id, the process group carries its 128 bytes to the others.  Returns (rank, nranks)."""
+    import torch
+    import torch.distributed as dist
+    rank, size = dist.get_rank(group), dist.get_world_size(group)
+    box = [kc.dist_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    torch.cuda.set_device(kc.device)
+    kc.dist_init(rank, size, box[0])
+    return rank, size
+
+
+class NativeUlyssesAttention:
+    """The sequence-parallel joint attention as ONE library call per step (krea_cuda_seqpar_joint_attention):
+    pack kernels, ncclSend/ncclRecv exchanges, the K normalisation pass overlapped with the exchange of V
+    and Q, the attention kernel and the exchange of the output all run inside libkrea_cuda."""
+
+    def __init__(self, kc, plan: UlyssesPlan):
+        if kc.dist_size() != plan.nranks:
+            raise ValueError(f"the handle's communicator has {kc.dist_size()} ranks, the plan {plan.nranks}")
+        self.kc, self.plan = kc, plan
+        self._out = None
+
+    def __call__(self, qkv_local, wq, wk, cos, sin, eps=1e-6, rope_mode=0, out=None):
+        """qkv_local: bf16 [rows_local, 3*heads*128]; returns bf16 [rows_local, heads*128]."""
+        import torch
+        plan, kc = self.plan, self.kc
+        H, ld = plan.heads, qkv_local.shape[-1]
+        if out is None:
+            if self._out is None:
+                self._out = torch.empty((plan.rows_local, H * HEAD_DIM), dtype=torch.bfloat16, device=qkv_local.device)
+            out = self._out
+        kc.set_stream(torch.cuda.current_stream())
+        flat = qkv_local.view(-1)
+        kc.seqpar_joint_attention(flat, flat[H * HEAD_DIM:], flat[2 * H * HEAD_DIM:], out, plan.seq, H, ld, ld, ld,
+                                  H * HEAD_DIM, wq, wk, cos, sin, eps, 1, rope_mode)
+        return out

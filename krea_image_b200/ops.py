@@ -146,6 +146,53 @@ class KreaCuda:
         self._check(self.lib.krea_cuda_reshard_unpack(self.h, ctypes.byref(a)))
 
 
+    # ---- sequence-parallel execution over NCCL -------------------------------------------------------
+    @staticmethod
+    def dist_unique_id() -> bytes:
+        """128 bytes that rank 0 creates and every rank passes to dist_init."""
+        lib = B.load()
+        buf = ctypes.create_string_buffer(B.DIST_ID_BYTES)
+        err = ctypes.create_string_buffer(512)
+        rc = lib.krea_cuda_dist_unique_id(ctypes.cast(buf, ctypes.c_void_p), err, 512)
+        if rc:
+            raise KreaCudaError(rc, err.value.decode() or "dist_unique_id failed")
+        return buf.raw
+
+    def dist_init(self, rank: int, nranks: int, uid: bytes):
+        """Collective over the nranks handles (one process and one handle per GPU)."""
+        if len(uid) != B.DIST_ID_BYTES:
+            raise ValueError(f"the id must be {B.DIST_ID_BYTES} bytes")
+        buf = ctypes.create_string_buffer(uid, B.DIST_ID_BYTES)
+        self._check(self.lib.krea_cuda_dist_init(self.h, rank, nranks, ctypes.cast(buf, ctypes.c_void_p)))
+
+    def dist_rank(self) -> int:
+        return int(self.lib.krea_cuda_dist_rank(self.h))
+
+    def dist_size(self) -> int:
+        return int(self.lib.krea_cuda_dist_size(self.h))
+
+    def dist_sync(self, timeout_ms: int = 0):
+        self._check(self.lib.krea_cuda_dist_sync(self.h, timeout_ms))
+
+    def dist_shutdown(self):
+        self._check(self.lib.krea_cuda_dist_shutdown(self.h))
+
+    def reshard_seq_to_heads(self, src, dst, rows_local, cols_per_rank, src_ld, src_col0=0):
+        a = B.A2AArgs(_ptr(src), _ptr(dst), rows_local, cols_per_rank, src_ld, 0, src_col0, 0)
+        self._check(self.lib.krea_cuda_reshard_seq_to_heads(self.h, ctypes.byref(a)))
+
+    def reshard_heads_to_seq(self, src, dst, rows_local, cols_per_rank, dst_ld, dst_col0=0):
+        a = B.A2AArgs(_ptr(src), _ptr(dst), rows_local, cols_per_rank, 0, dst_ld, 0, dst_col0)
+        self._check(self.lib.krea_cuda_reshard_heads_to_seq(self.h, ctypes.byref(a)))
+
+    def seqpar_joint_attention(self, Q, K, V, O, seq, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps=1e-6, group=1,
+                               rope_mode=B.ROPE_PAIRS):
+        """Q, K, V, O: this rank's rows [seq / nranks] of every head; cos/sin: the global tables."""
+        a = B.SeqParArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), seq, heads, group, ldq, ldk, ldv, ldo,
+                         _ptr(wq), _ptr(wk), _ptr(cos), _ptr(sin), eps, rope_mode)
+        self._check(self.lib.krea_cuda_seqpar_joint_attention(self.h, ctypes.byref(a)))
+
+
 def rope_tables_ref3axis(T, gh, gw):
     """DiT::set_grid (engine/src/model.mm:290-315): numpy f32 cos/sin [T + gh*gw, 64] built by the library."""
     import numpy as np

@@ -3,7 +3,8 @@
 * head sharding: each rank runs the single-GPU kernel on its heads, no data-path collective; the
   concatenation equals the single-GPU result bit for bit and matches the oracle.
 * sequence parallel (Ulysses): rows start sharded, all-to-all to heads, fused call, all-to-all back; every
-  rank's rows match the oracle within the parity tolerance.
+  rank's rows match the oracle within the parity tolerance - once with torch.distributed carrying the
+  all-to-all and once through the library's own NCCL communicator (one C call per step), bit-identical.
 """
 import os
 import socket
@@ -78,6 +79,29 @@ def _worker(rank, world, port, out_dir):
         rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
         assert rel <= 5e-3 and np.abs(got - ref).max() <= 2e-2, f"ulysses rank {rank}: {rel}"
         assert torch.equal(out.view(torch.int16), o_all[lo:hi].contiguous().view(torch.int16))   # same kernels, same bits
+
+        # ---- the same through the library's own NCCL communicator: one C call per step ----
+        assert kc.dist_size() == 0 and kc.dist_rank() == -1
+        assert kd.init_native(kc) == (rank, world)
+        assert kc.dist_size() == world and kc.dist_rank() == rank
+        na = kd.NativeUlyssesAttention(kc, plan)
+        xl = x[lo:hi].contiguous()
+        for _ in range(2):   # the second call reuses the workspace
+            out2 = na(xl, d_wq, d_wk, d_cos, d_sin)
+            kc.dist_sync(60000)
+            assert torch.equal(out2.view(torch.int16), out.view(torch.int16))
+        # the two exchanges on their own: there and back again
+        rl, cl = plan.rows_local, plan.cols_local
+        q_heads = torch.zeros((S, cl), dtype=torch.bfloat16, device="cuda")
+        kc.reshard_seq_to_heads(xl, q_heads, rl, cl, ld, 0)
+        kc.dist_sync(60000)
+        assert torch.equal(q_heads.view(torch.int16), x[:, rank * cl:(rank + 1) * cl].contiguous().view(torch.int16))
+        back = torch.zeros((rl, H * 128), dtype=torch.bfloat16, device="cuda")
+        kc.reshard_heads_to_seq(q_heads, back, rl, cl, H * 128, 0)
+        kc.dist_sync(60000)
+        assert torch.equal(back.view(torch.int16), xl[:, :H * 128].contiguous().view(torch.int16))
+        kc.dist_shutdown()
+        assert kc.dist_size() == 0
         kc.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:

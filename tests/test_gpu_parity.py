@@ -317,6 +317,48 @@ def test_host_entry_pipelined_over_head_groups(kc):
     assert np.array_equal(got, got_dev)
 
 
+def test_sequence_parallel_entry_points_on_one_rank(kc):
+    """The library's NCCL path with a communicator of one rank: the exchanges are self-sends, and the
+    sequence-parallel call must reproduce the single-GPU fused call bit for bit."""
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    H, T, gh, gw = 3, 64, 10, 16
+    S = T + gh * gw
+    qkv, wq, wk, cos, sin = rand_case(91, 1, S, H, T, gh, gw)
+    ld = 3 * H * 128
+    x = dev_bits(qkv).view(S, ld)
+    dw = (dev_f32(wq), dev_f32(wk), dev_f32(cos), dev_f32(sin))
+    o_ref = torch.zeros((S, H * 128), dtype=torch.bfloat16, device="cuda")
+    xf = x.view(-1)
+    kc.joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o_ref, S, S, H, ld, ld, ld, H * 128, *dw)
+    kc.wait()
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.seqpar_joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o_ref, S, H, ld, ld, ld, H * 128, *dw)
+    assert e.value.code == binding.E_COMM          # no communicator yet
+    kc.dist_init(0, 1, ops.KreaCuda.dist_unique_id())
+    try:
+        assert (kc.dist_rank(), kc.dist_size()) == (0, 1)
+        o = torch.full((S, H * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        n0 = kc.launches
+        kc.seqpar_joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o, S, H, ld, ld, ld, H * 128, *dw)
+        kc.dist_sync(60000)
+        assert kc.launches - n0 == 6         # three packs, K pre-pass, attention, unpack
+        assert torch.equal(o.view(torch.int16), o_ref.view(torch.int16))
+        heads = torch.zeros((S, H * 128), dtype=torch.bfloat16, device="cuda")
+        kc.reshard_seq_to_heads(x, heads, S, H * 128, ld, H * 128)          # the K columns
+        back = torch.zeros((S, ld), dtype=torch.bfloat16, device="cuda")
+        kc.reshard_heads_to_seq(heads, back, S, H * 128, ld, 2 * H * 128)    # ... into the V columns
+        kc.dist_sync(60000)
+        assert torch.equal(heads.view(torch.int16), x[:, H * 128:2 * H * 128].contiguous().view(torch.int16))
+        assert torch.equal(back[:, 2 * H * 128:].contiguous().view(torch.int16), heads.view(torch.int16))
+        with pytest.raises(ops.KreaCudaError):     # heads not a multiple of 8 columns / bad leading dimension
+            kc.reshard_seq_to_heads(x, heads, S, H * 128, ld + 4, 0)
+        with pytest.raises(ops.KreaCudaError):
+            kc.seqpar_joint_attention(xf, xf, xf, o, S, H, ld, ld, ld, 64, *dw)
+    finally:
+        kc.dist_shutdown()
+    assert kc.dist_size() == 0
+
+
 def test_argument_errors_launch_nothing(kc):
     n0 = kc.launches
     t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")

@@ -238,6 +238,13 @@ def run_ours(args, rank, world, local_rank):
     kc = ops.KreaCuda(local_rank)          # no fallback: raises if the CUDA library cannot be loaded
     stream = torch.cuda.current_stream()
     kc.set_stream(stream)
+    # units of work: whole samples per GPU (weak scaling), or this rank's heads of the one problem (strong
+    # scaling; heads are independent, so there is still no data-path collective)
+    by_heads = args.shard == "heads" and world > 1
+    if by_heads and H % world:
+        raise SystemExit(f"--shard heads: {H} heads do not split over {world} GPUs")
+    Hl = H // world if by_heads else H
+    h0 = rank * Hl if by_heads else 0
 
     # ---- seeded synthetic inputs, pinned on the host and resident on the device ----
     qkv_h = torch.from_numpy(synth.qkv_slice(cfg).view(np.int16)).pin_memory()
@@ -258,7 +265,8 @@ def run_ours(args, rank, world, local_rank):
 
     def step(i):
         x, o = xs[i % nsets], os_[i % nsets]
-        kc.joint_attention(x, x[H * 128:], x[2 * H * 128:], o, S, S, H, ld, ld, ld, H * 128, d_wq, d_wk, d_cos, d_sin, 1e-6, 1, 0, 0,
+        kc.joint_attention(x[h0 * 128:], x[(H + h0) * 128:], x[(2 * H + h0) * 128:], o.view(-1)[h0 * 128:], S, S, Hl, ld, ld, ld, H * 128,
+                           d_wq, d_wk, d_cos, d_sin, 1e-6, 1, 0, 0,
                            batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=d_tl, text_slots=cfg.text if tl is not None else 0)
 
     def barrier():
@@ -315,7 +323,8 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end through the host-pointer entry point ----
     q_h = qkv_h.view(-1)
-    e2e_args = (q_h, q_h[H * 128:], q_h[2 * H * 128:], out_h, S, S, H, ld, ld, ld, H * 128, wq, wk, cos, sin)
+    e2e_args = (q_h[h0 * 128:], q_h[(H + h0) * 128:], q_h[(2 * H + h0) * 128:], out_h.view(-1)[h0 * 128:], S, S, Hl, ld, ld, ld, H * 128,
+                wq, wk, cos, sin)
     e2e_kw = dict(batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=tl, text_slots=cfg.text if tl is not None else 0)
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -327,25 +336,27 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
     checksum = int(out_h.view(-1)[:: max(1, out_h.numel() // 4096)].to(torch.int64).sum().item())
-    h2d = in_bytes + 2 * cos.nbytes + 1024 + (tl.nbytes if tl is not None else 0)
+    h2d = in_bytes * Hl // H + 2 * cos.nbytes + 1024 + (tl.nbytes if tl is not None else 0)
+    d2h = out_bytes * Hl // H
 
     if rank == 0:
         peak, peak_sustained, peak_kind = measured_peaks()
-        value = world * flops / (ms_step * 1e-3) / 1e12
-        attn_tflops = flops / (attn_ms_avg * 1e-3) / 1e12
+        job_flops = flops if by_heads else world * flops     # all ranks together, per step
+        value = job_flops / (ms_step * 1e-3) / 1e12
+        attn_tflops = job_flops / world / (attn_ms_avg * 1e-3) / 1e12
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "metric": METRIC if cfg.cid == 1 else f"joint-attn TFLOP/s at S={S}, B={B}, 24 heads, head_dim 128", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": cfg.name, "batch": cfg.batch, "heads": H, "seq": S, "head_dim": 128, "per_gpu": "one full sample (all heads)",
+            "config": {"workload": cfg.name, "batch": cfg.batch, "heads": H, "seq": S, "head_dim": 128, "per_gpu": f"heads [{h0}, {h0 + Hl}) of rank 0; {Hl} heads per GPU, no collective" if by_heads else "one full problem (all heads)",
                        "l2": f"rotating {nsets} input/output sets ({nsets * (in_bytes + out_bytes) / 1e6:.0f} MB > 126 MB L2)",
-                       "flops_per_step_per_gpu": flops},
+                       "flops_per_step_per_gpu": job_flops / world},
             "pct_of_measured_bf16_peak": 100.0 * value / world / peak,
             "pct_of_nominal_bf16_peak": 100.0 * value / world / 2250.0,
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(out_bytes), "ms_per_step": e2e_ms, "steps": e2e_steps, "checksum": checksum},
+            "e2e": {"value": job_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps, "checksum": checksum},
             "roofline": {"bound": "tensor", "achieved": attn_tflops, "peak": peak, "unit": "TFLOP/s", "frac": attn_tflops / peak,
                          "traffic": ATTN_DRAM_TRAFFIC_BYTES.get(cfg.cid), "peak_kind": f"{peak_kind} burst bf16 GEMM",
                          "frac_of_sustained": attn_tflops / peak_sustained, "kernel": "attn_fwd_sm100", "kernel_ms": attn_ms_avg,
@@ -368,6 +379,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--shard", default="samples", choices=["samples", "heads"],
+                    help="several GPUs, workloads c0-c3: every GPU runs a whole problem (weak scaling), or its share of the heads of one problem (strong)")
     ap.add_argument("--a2a", default="native", choices=["native", "torch"],
                     help="workload c4 on several GPUs: who carries the all-to-all (the library's NCCL communicator, or torch.distributed)")
     args = ap.parse_args()

@@ -196,6 +196,20 @@ KREA_CUDA_API int krea_cuda_joint_attention_host(krea_cuda* h, const krea_cuda_j
 KREA_CUDA_API int krea_cuda_rope_tables_ref3axis(float* cos, float* sin, int T, int gh, int gw);
 KREA_CUDA_API int krea_cuda_rope_tables_axial2d(float* cos, float* sin, int T, int gh, int gw, double theta);
 
+/* ---- Metal::layerwise_attn (engine/src/metal.h:90-91, metal.mm:204-209; kernel norm.metal:136-178) ----
+ * The text fusion's attention across the 12 tapped encoder states of each token.  Rows are token-major
+ * (row = t*12 + j) in a fused bf16 [q | k | v | gate] buffer with `ld` columns, heads of 128 channels at
+ * the four column offsets; out[row, h*128 + d] = softmax_j(q[row] . k[base+j] / sqrt(128)) v[base+j] *
+ * sigmoid(gate[row]), fp32 inside, bf16 store.  Same argument order and units as the reference's method;
+ * rows must be a multiple of 12 (the reference would read past the buffer otherwise). */
+typedef struct {
+  const void* qkvg;
+  void* out;
+  int rows, ld, ldo, heads;
+  int q_off, k_off, v_off, g_off;
+} krea_cuda_layerwise_args;
+KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwise_args* a);
+
 /* ---- sequence-parallel resharding helpers (no counterpart in the reference, which is single-device) ----
  * Pack / unpack kernels either side of an all-to-all that turns sequence-sharded rows (all heads, rows
  * [r*S/P, (r+1)*S/P)) into head-sharded rows (all S rows, heads [r*H/P, (r+1)*H/P)) and back.

@@ -50,6 +50,11 @@ class ReshardArgs(ctypes.Structure):
                 ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
 
 
+class LayerwiseArgs(ctypes.Structure):
+    _fields_ = [("qkvg", _vp), ("out", _vp), ("rows", _int), ("ld", _int), ("ldo", _int), ("heads", _int),
+                ("q_off", _int), ("k_off", _int), ("v_off", _int), ("g_off", _int)]
+
+
 class A2AArgs(ctypes.Structure):
     _fields_ = [("src", _vp), ("dst", _vp), ("rows_local", _int), ("cols_per_rank", _int),
                 ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
@@ -80,6 +85,7 @@ SYMBOLS = {
     "krea_cuda_joint_attention_static": (_int, [_vp, ctypes.POINTER(JointArgs)]),
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
+    "krea_cuda_layerwise_attn": (_int, [_vp, ctypes.POINTER(LayerwiseArgs)]),
     "krea_cuda_reshard_pack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_reshard_unpack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_dist_unique_id": (_int, [_vp, ctypes.c_char_p, _int]),

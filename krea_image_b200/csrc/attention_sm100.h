@@ -78,4 +78,15 @@ struct ReshardParams {
 cudaError_t launch_reshard_pack(const ReshardParams& p, cudaStream_t stream);
 cudaError_t launch_reshard_unpack(const ReshardParams& p, cudaStream_t stream);
 
+// The text fusion's 12-tap attention (norm.metal:141-145 LayerAttnParams): rows = tokens * 12.
+struct LayerwiseParams {
+  const __nv_bfloat16* qkvg;
+  __nv_bfloat16* out;
+  int rows, heads;
+  int64_t ld, ldo;
+  int q_off, k_off, v_off, g_off;
+  float scale;
+};
+cudaError_t launch_layerwise_attn(const LayerwiseParams& p, cudaStream_t stream);
+
 }  // namespace krea

@@ -721,6 +721,30 @@ static int reshard(krea_cuda* h, const krea_cuda_reshard_args* a, bool unpack) {
   h->launches++;
   return KREA_CUDA_OK;
 }
+int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwise_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "layerwise_attn: null handle or arguments");
+  if (a->rows < 0 || a->heads < 0 || a->rows % 12) return fail(h, KREA_CUDA_E_ARG, "layerwise_attn: rows (%d) must be a non-negative multiple of 12", a->rows);
+  if (a->rows == 0 || a->heads == 0) return KREA_CUDA_OK;
+  if (!a->qkvg || !a->out || !aligned16(a->qkvg) || !aligned16(a->out)) return fail(h, KREA_CUDA_E_ARG, "layerwise_attn: null or misaligned pointer");
+  const int offs[4] = {a->q_off, a->k_off, a->v_off, a->g_off};
+  for (int o : offs)
+    if (o < 0 || o % 8 || (int64_t)o + (int64_t)a->heads * 128 > a->ld) return fail(h, KREA_CUDA_E_ARG, "layerwise_attn: column offset %d does not fit %d heads inside ld %d (offsets are multiples of 8)", o, a->heads, a->ld);
+  if (a->ld % 8 || a->ldo % 8 || a->ldo < a->heads * 128) return fail(h, KREA_CUDA_E_ARG, "layerwise_attn: leading dimensions must be multiples of 8 and ldo must cover all heads");
+  LayerwiseParams p{};
+  p.qkvg = (const __nv_bfloat16*)a->qkvg;
+  p.out = (__nv_bfloat16*)a->out;
+  p.rows = a->rows;
+  p.heads = a->heads;
+  p.ld = a->ld;
+  p.ldo = a->ldo;
+  p.q_off = a->q_off; p.k_off = a->k_off; p.v_off = a->v_off; p.g_off = a->g_off;
+  p.scale = (float)(1.0 / sqrt(128.0));   // metal.mm:206
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, launch_layerwise_attn(p, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+
 int krea_cuda_reshard_pack(krea_cuda* h, const krea_cuda_reshard_args* a) { return reshard(h, a, false); }
 int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a) { return reshard(h, a, true); }
 

@@ -136,6 +136,11 @@ class KreaCuda:
         a.Lk, a.heads, a.group, a.batch = Lk, heads, group, batch
         return int(self.lib.krea_cuda_joint_scratch_bytes(ctypes.byref(a)))
 
+    def layerwise_attn(self, qkvg, out, rows, ld, ldo, heads, q_off, k_off, v_off, g_off):
+        """Metal::layerwise_attn (engine/src/metal.h:90-91): same argument order."""
+        a = B.LayerwiseArgs(_ptr(qkvg), _ptr(out), rows, ld, ldo, heads, q_off, k_off, v_off, g_off)
+        self._check(self.lib.krea_cuda_layerwise_attn(self.h, ctypes.byref(a)))
+
     # ---- sequence <-> head resharding ---------------------------------------------------------------
     def reshard_pack(self, src, dst, nranks, rows, cols_per_rank, src_ld, src_col0=0):
         a = B.ReshardArgs(_ptr(src), _ptr(dst), nranks, rows, cols_per_rank, src_ld, 0, src_col0, 0)

@@ -145,3 +145,11 @@ def joint_attention_rows(qkv_b, S, heads, h, wq, wk, cos, sin, rows_sel, eps=1e-
                                   _p(wq, _f32p), _p(wk, _f32p), _p(cos, _f32p), _p(sin, _f32p), ctypes.c_float(eps),
                                   rope_mode, text_len, text_slots, _p(rs, _i32p), len(rs), int(ref_rounding))
     return out
+
+
+def layerwise_attn(qkvg, rows, ld, heads, q_off, k_off, v_off, g_off, ref_rounding=False):
+    """The text fusion's 12-tap attention (norm.metal:136-178).  qkvg: uint16 [rows, ld]; fp32 [rows, heads*128]."""
+    assert qkvg.dtype == np.uint16 and qkvg.flags["C_CONTIGUOUS"] and rows % 12 == 0
+    out = np.zeros((rows, heads * 128), dtype=np.float32)
+    lib().ko_layerwise_attn(_p(qkvg, _u16p), _p(out, _f32p), rows, ld, heads, q_off, k_off, v_off, g_off, int(ref_rounding))
+    return out

@@ -379,3 +379,44 @@ void ko_joint_attention_rows(const uint16_t* Q, const uint16_t* K, const uint16_
   }
   free(q); free(kt); free(v); free(valid);
 }
+
+/* ---- text-fusion layerwise attention (norm.metal:136-178, dispatch metal.mm:204-209) ----
+ * Rows are token-major, row = t*12 + j; every row attends over the 12 rows of its own token:
+ *   out[row, h*128 + d] = softmax_j(q[row] . k[base+j] / sqrt(128)) v[base+j] * sigmoid(gate[row])
+ * with scores, softmax and the weighted sum in fp32 (P is NOT rounded here, unlike attn_body) and one
+ * bf16 rounding at the store.  qkvg: fused bf16 rows [rows, ld], heads of 128 channels at q_off, k_off,
+ * v_off, g_off.  Output fp32 [rows, heads*128]; ref_rounding rounds it to bf16. */
+void ko_layerwise_attn(const uint16_t* qkvg, float* out, int rows, int ld, int heads, int q_off, int k_off, int v_off,
+                       int g_off, int ref_rounding) {
+  const int taps = 12;
+  const float scale = (float)(1.0 / sqrt(128.0));
+#pragma omp parallel for schedule(static)
+  for (int row = 0; row < rows; row++) {
+    const int base = row - row % taps;
+    for (int h = 0; h < heads; h++) {
+      const uint16_t* q = qkvg + (size_t)row * ld + q_off + h * KO_D;
+      float s[12], mx = -INFINITY;
+      for (int j = 0; j < taps; j++) {
+        const uint16_t* k = qkvg + (size_t)(base + j) * ld + k_off + h * KO_D;
+        double acc = 0.0;
+        for (int d = 0; d < KO_D; d++) acc += (double)bf16_to_f32(q[d]) * (double)bf16_to_f32(k[d]);
+        s[j] = (float)acc * scale;
+        if (s[j] > mx) mx = s[j];
+      }
+      float l = 0.f, o[KO_D];
+      for (int d = 0; d < KO_D; d++) o[d] = 0.f;
+      for (int j = 0; j < taps; j++) {
+        const float e = expf(s[j] - mx);
+        l += e;
+        const uint16_t* v = qkvg + (size_t)(base + j) * ld + v_off + h * KO_D;
+        for (int d = 0; d < KO_D; d++) o[d] += e * bf16_to_f32(v[d]);
+      }
+      const uint16_t* g = qkvg + (size_t)row * ld + g_off + h * KO_D;
+      float* dst = out + (size_t)row * heads * KO_D + (size_t)h * KO_D;
+      for (int d = 0; d < KO_D; d++) {
+        const float r = o[d] / l * (1.0f / (1.0f + expf(-bf16_to_f32(g[d]))));
+        dst[d] = ref_rounding ? bf16_round(r) : r;
+      }
+    }
+  }
+}

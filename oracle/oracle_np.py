@@ -78,3 +78,17 @@ def joint_attention(qkv_bits, B, S, heads, wq, wk, cos, sin, eps=1e-6, rope_mode
                 o[~key_ok] = 0.0
             out[b, :, h] = round_bf16(o) if ref_rounding else o
     return out.reshape(B, S, heads * 128)
+
+
+def layerwise_attn(qkvg_bits, rows, ld, heads, q_off, k_off, v_off, g_off):
+    """float64 statement of the 12-tap attention: each row attends over the 12 rows of its token."""
+    x = bf16_bits_to_f64(qkvg_bits).reshape(rows // 12, 12, ld)
+
+    def blk(off):
+        return x[:, :, off:off + heads * 128].reshape(-1, 12, heads, 128)
+    q, k, v, g = blk(q_off), blk(k_off), blk(v_off), blk(g_off)
+    s = np.einsum("tihd,tjhd->thij", q, k) / np.sqrt(128.0)
+    p = np.exp(s - s.max(axis=-1, keepdims=True))
+    p /= p.sum(axis=-1, keepdims=True)
+    o = np.einsum("thij,tjhd->tihd", p, v) / (1.0 + np.exp(-g))
+    return o.reshape(rows, heads * 128)

@@ -317,6 +317,30 @@ def test_host_entry_pipelined_over_head_groups(kc):
     assert np.array_equal(got, got_dev)
 
 
+@pytest.mark.parametrize("T,H", [(1, 1), (77, 5), (512, 20)])
+def test_layerwise_attn_operator(kc, T, H):
+    """Metal::layerwise_attn (metal.mm:204-209): the text fusion's attention over the 12 taps of each token,
+    in the caller's layout (model.mm:197: q | k | v | gate blocks of one fused row)."""
+    rng = np.random.default_rng(T * 31 + H)
+    rows, ld = T * 12, 4 * H * 128
+    x = synth.f32_to_bf16_bits((1.5 * rng.standard_normal((rows, ld))).astype(np.float32))
+    offs = (0, H * 128, 2 * H * 128, 3 * H * 128)
+    want = oracle.layerwise_attn(x, rows, ld, H, *offs)
+    want_r = oracle.layerwise_attn(x, rows, ld, H, *offs, ref_rounding=True)
+    o = torch.full((rows, H * 128 + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    n0 = kc.launches
+    kc.layerwise_attn(dev_bits(x), o, rows, ld, H * 128 + 8, H, *offs)
+    kc.wait()
+    assert kc.launches - n0 == 1
+    got = host_f32(o)
+    check(got[:, :H * 128], want, want_r, f"layerwise T={T} H={H}")
+    assert np.all(np.isnan(got[:, H * 128:]))                       # nothing written outside the head columns
+    with pytest.raises(ops.KreaCudaError):
+        kc.layerwise_attn(dev_bits(x), o, rows - 1, ld, H * 128 + 8, H, *offs)   # not a multiple of 12
+    with pytest.raises(ops.KreaCudaError):
+        kc.layerwise_attn(dev_bits(x), o, rows, ld, H * 128 + 8, H, 0, H * 128, 2 * H * 128, 3 * H * 128 + 8)   # gate block past ld
+
+
 def test_sequence_parallel_entry_points_on_one_rank(kc):
     """The library's NCCL path with a communicator of one rank: the exchanges are self-sends, and the
     sequence-parallel call must reproduce the single-GPU fused call bit for bit."""

@@ -263,6 +263,26 @@ def test_head_slices_equal_columns_of_the_full_tensor():
     assert np.array_equal(full[:, 5:105, :, 3:5].reshape(1, 100, -1), part)
 
 
+def test_layerwise_attn_vs_numpy_and_closed_form():
+    """The text fusion's 12-tap attention (norm.metal:136-178) against the float64 statement, plus a closed
+    form: identical taps give uniform weights, so the output is the tap's v row times sigmoid(gate)."""
+    rng = np.random.default_rng(5)
+    T, H = 7, 3
+    rows, ld = T * 12, 4 * H * 128 + 16
+    offs = (8, 8 + H * 128, 8 + 2 * H * 128, 16 + 3 * H * 128)
+    x = synth.f32_to_bf16_bits(rng.standard_normal((rows, ld)).astype(np.float32))
+    a = oracle.layerwise_attn(x, rows, ld, H, *offs)
+    b = oracle_np.layerwise_attn(x, rows, ld, H, *offs)
+    assert np.abs(a - b).max() < 2e-6
+    r = oracle.layerwise_attn(x, rows, ld, H, *offs, ref_rounding=True)
+    assert np.array_equal(r, oracle.bf16_to_f32(oracle.f32_to_bf16(a)))
+    x[:] = x[0]                                            # every row the same
+    a = oracle.layerwise_attn(x, rows, ld, H, *offs)
+    xf = synth.bf16_bits_to_f32(x[0])
+    want = xf[offs[2]:offs[2] + H * 128] / (1.0 + np.exp(-xf[offs[3]:offs[3] + H * 128]))
+    assert np.allclose(a, want[None], atol=1e-6)
+
+
 def test_flop_count():
     assert synth.attention_flops(synth.CONFIGS[1]) == pytest.approx(2.6092e11, rel=1e-4)
     assert synth.attention_flops(synth.CONFIGS[0]) == pytest.approx(2.899e10, rel=1e-3)

@@ -169,6 +169,8 @@ def run_seq_parallel(args, rank, world, local_rank):
     flops = synth.attention_flops(cfg)
     if world > 1 and args.a2a == "native":
         kd.init_native(kc)                     # the library's own NCCL communicator: one C call per step
+        exchange = {"p2p": "peer stores over NVLink inside libkrea_cuda (pack kernels and attention epilogue), NCCL barriers",
+                    "nccl": "ncclSend/ncclRecv inside libkrea_cuda"}[kc.dist_exchange_mode()]
         ua = kd.NativeUlyssesAttention(kc, plan)
         step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
     elif world > 1:
@@ -216,7 +218,7 @@ def run_seq_parallel(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": cfg.name, "batch": 1, "heads": H, "seq": S, "head_dim": 128,
                        "parallelism": f"sequence-sharded in/out, all-to-all to {H // world} heads per GPU" if world > 1 else "single GPU",
-                       "exchange": ("ncclSend/ncclRecv inside libkrea_cuda" if args.a2a == "native" else "torch.distributed all_to_all_single") if world > 1 else None,
+                       "exchange": (exchange if args.a2a == "native" else "torch.distributed all_to_all_single") if world > 1 else None,
                        "l2": "inputs (1.2 GB) exceed the 126 MB L2"},
             "pct_of_measured_bf16_peak": 100.0 * value / world / peak, "gpu_launches": int(launches), "clocks": clocks,
             "e2e": None, "roofline": None}))

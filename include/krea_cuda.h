@@ -248,6 +248,13 @@ KREA_CUDA_API int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard
 #define KREA_CUDA_DIST_ID_BYTES 128
 KREA_CUDA_API int krea_cuda_dist_unique_id(void* id_out /* KREA_CUDA_DIST_ID_BYTES */, char* err, int errlen);
 KREA_CUDA_API int krea_cuda_dist_init(krea_cuda* h, int rank, int nranks, const void* id);
+/* How krea_cuda_seqpar_joint_attention moves rows between ranks: 1 = peer stores (every rank's workspace is
+ * mapped into every process with CUDA IPC; the pack kernels and the attention epilogue store straight into
+ * the destination GPU's memory over NVLink and NCCL only provides the barriers in between), 0 = NCCL
+ * transfers (ncclSend/ncclRecv between staging buffers), -1 = no communicator.  Peer stores are the
+ * default for 2 to 8 ranks; set the environment variable KREA_CUDA_SEQPAR_EXCHANGE=nccl (identically on
+ * every rank) to force NCCL transfers, which are also used when a mapping cannot be made. */
+KREA_CUDA_API int krea_cuda_dist_exchange_mode(krea_cuda* h);
 KREA_CUDA_API int krea_cuda_dist_rank(krea_cuda* h);    /* -1 before krea_cuda_dist_init */
 KREA_CUDA_API int krea_cuda_dist_size(krea_cuda* h);    /* 0 before krea_cuda_dist_init */
 /* Waits for the handle's stream for at most timeout_ms (<= 0: no limit), polling the communicator for
@@ -270,9 +277,11 @@ KREA_CUDA_API int krea_cuda_reshard_seq_to_heads(krea_cuda* h, const krea_cuda_a
 /* dst[i][dst_col0 + p*cols_per_rank + c] = (rank p's src)[rank*rows_local + i][c] */
 KREA_CUDA_API int krea_cuda_reshard_heads_to_seq(krea_cuda* h, const krea_cuda_a2a_args* a);
 
-/* The fused call on sequence-sharded rows: three exchanges (K first, so that its normalisation pass
- * overlaps the exchange of V and Q on a second stream), the joint attention on the local heads, and
- * the exchange of the output back.  Q, K, V: local rows [rows_local][ld*] holding all `heads` (K, V:
+/* The fused call on sequence-sharded rows: Q, K and V rows travel to the ranks that own their heads, the
+ * joint attention runs on the local heads, and the output rows travel home.  With peer stores the
+ * attention kernel's epilogue itself writes every output row into its home rank's memory; with NCCL
+ * transfers K travels first, so that its normalisation pass overlaps the exchange of V and Q on a second
+ * stream.  Q, K, V: local rows [rows_local][ld*] holding all `heads` (K, V:
  * heads/group) heads; O: local rows [rows_local][ldo], all heads.  cos/sin: the global tables
  * [seq][64].  batch, the padding mask and the gate are not supported here.  Workspace (about six
  * times seq * heads/nranks * 256 bytes) is owned by the handle and grown on demand. */

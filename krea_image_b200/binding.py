@@ -90,6 +90,7 @@ SYMBOLS = {
     "krea_cuda_reshard_unpack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_dist_unique_id": (_int, [_vp, ctypes.c_char_p, _int]),
     "krea_cuda_dist_init": (_int, [_vp, _int, _int, _vp]),
+    "krea_cuda_dist_exchange_mode": (_int, [_vp]),
     "krea_cuda_dist_rank": (_int, [_vp]),
     "krea_cuda_dist_size": (_int, [_vp]),
     "krea_cuda_dist_sync": (_int, [_vp, _int]),

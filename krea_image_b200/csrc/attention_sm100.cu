@@ -91,6 +91,18 @@ struct Cfg {
   static_assert(REGS_LAUNCH * THREADS == NQ * SM_THREADS * REGS_SOFTMAX + 128 * REGS_OTHER, "register budget must add up");
 };
 
+// Start of output row `grow` (column 0 of sample 0): O + grow * ldo, or, with the row-block scatter, the
+// row's place under its block's base pointer.  The block table sits in kernel parameter space, which wants
+// compile-time indices: a chain of selects, not an indexed load.
+__device__ __forceinline__ __nv_bfloat16* out_row(const AttnParams& p, int grow) {
+  if (p.o_blk_rows <= 0) return p.O + (size_t)grow * p.ldo;
+  const int blk = grow / p.o_blk_rows;
+  __nv_bfloat16* base = p.O_blk[0];
+#pragma unroll
+  for (int k = 1; k < 8; k++) base = blk == k ? p.O_blk[k] : base;
+  return base + (size_t)(grow - blk * p.o_blk_rows) * p.ldo;
+}
+
 // First / one-past-last fully masked key tile for padding range [lo, hi).
 __device__ __forceinline__ void skip_range(int lo, int hi, int& first, int& end) {
   first = (lo + BN - 1) / BN;
@@ -497,19 +509,19 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       {
         const int sub = lane >> 4, ch = lane & 15;
         constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;
-        __nv_bfloat16* obase = p.O + (size_t)b * p.bso + (size_t)h * D + 8 * ch;
+        const size_t ocol = (size_t)b * p.bso + (size_t)h * D + 8 * ch;
 #pragma unroll 4
         for (int it = 0; it < ROWS_PER_WARP / 2; it++) {
           const int rr = wt * ROWS_PER_WARP + it * 2 + sub;
           const int grow = q0 + g * BM + rr;
           const uint4 v = *(const uint4*)(ostage + rr * 256 + ((ch ^ (rr & 15)) << 4));
-          if (grow < p.Lq) *(uint4*)(obase + (size_t)grow * p.ldo) = v;
+          if (grow < p.Lq) *(uint4*)(out_row(p, grow) + ocol) = v;
         }
       }
       KTRACE(trace_me, 30 + g, 2);
     } else if (tile_active && row < p.Lq && part == 0) {
       // no visible key at all: zeros
-      uint4* dst = (uint4*)(p.O + (size_t)b * p.bso + (size_t)row * p.ldo + (size_t)h * D);
+      uint4* dst = (uint4*)(out_row(p, row) + (size_t)b * p.bso + (size_t)h * D);
 #pragma unroll
       for (int c = 0; c < 16; c++) dst[c] = make_uint4(0u, 0u, 0u, 0u);
     }

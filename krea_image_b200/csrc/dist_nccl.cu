@@ -33,6 +33,8 @@ struct NcclApi {
   decltype(&ncclGroupEnd) GroupEnd = nullptr;
   decltype(&ncclSend) Send = nullptr;
   decltype(&ncclRecv) Recv = nullptr;
+  decltype(&ncclAllReduce) AllReduce = nullptr;
+  decltype(&ncclAllGather) AllGather = nullptr;
   std::string why;   // why loading failed
 };
 
@@ -71,6 +73,8 @@ const NcclApi* nccl_api() {
   a.GroupEnd = (decltype(a.GroupEnd))sym("ncclGroupEnd");
   a.Send = (decltype(a.Send))sym("ncclSend");
   a.Recv = (decltype(a.Recv))sym("ncclRecv");
+  a.AllReduce = (decltype(a.AllReduce))sym("ncclAllReduce");
+  a.AllGather = (decltype(a.AllGather))sym("ncclAllGather");
   if (!ok) {
     dlclose(lib);
     return nullptr;
@@ -90,6 +94,14 @@ struct KreaDist {
   size_t ws_bytes = 0;
   cudaStream_t side = nullptr;   // second stream: exchanges that overlap the K normalisation pass
   cudaEvent_t ev[4] = {};        // 0 start, 1 K landed, 2 Q and V landed, 3 spare
+  // Peer-store mode: every rank's workspace is mapped into every other rank's process (CUDA IPC), the pack
+  // kernels and the attention epilogue store straight into the destination rank's memory over NVLink, and
+  // NCCL only provides the barriers in between.
+  bool p2p = false;              // agreed by all ranks at init
+  void* sym = nullptr;           // this rank's symmetric workspace
+  size_t sym_bytes = 0;
+  void* peer[8] = {};            // peer[r]: rank r's symmetric workspace as seen from this process (peer[rank] == sym)
+  unsigned char* xchg = nullptr; // device scratch: 8 IPC handles + the barrier word
 };
 
 #define NCCL_TRY(h, d, expr)                                                                               \
@@ -173,6 +185,76 @@ static int heads_to_seq_on(krea_cuda* h, const void* src, void* dst, void* stage
   return KREA_CUDA_OK;
 }
 
+// ---- peer-store mode ---------------------------------------------------------------------------------
+constexpr size_t XCHG_BYTES = 8 * sizeof(cudaIpcMemHandle_t) + 256;
+
+// All ranks reach this point of their streams: a one-float all-reduce.  Stream-ordered; kernels enqueued
+// after it on any rank start only after every rank's earlier kernels (and their peer stores) have completed.
+static int rank_barrier(krea_cuda* h, cudaStream_t stream, ncclRedOp_t op = ncclSum) {
+  KreaDist* d = h->dist;
+  float* w = (float*)(d->xchg + 8 * sizeof(cudaIpcMemHandle_t));
+  NCCL_TRY(h, d, d->api->AllReduce(w, w, 1, ncclFloat, op, d->comm, stream));
+  return KREA_CUDA_OK;
+}
+
+static void close_peers(KreaDist* d) {
+  for (int r = 0; r < 8; r++) {
+    if (d->peer[r] && r != d->rank) cudaIpcCloseMemHandle(d->peer[r]);
+    d->peer[r] = nullptr;
+  }
+}
+
+// (Re)allocates the symmetric workspace and maps every rank's copy.  Collective: every rank calls it with
+// the same size at the same point of its call sequence.  Returns KREA_CUDA_OK with d->p2p possibly cleared
+// (all ranks agree) when a mapping could not be made.
+static int sym_alloc(krea_cuda* h, size_t bytes) {
+  KreaDist* d = h->dist;
+  // nobody may still be storing into the old block, and nobody may keep a mapping of it
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  CUDA_TRY(h, cudaStreamSynchronize(d->side));
+  int rc = rank_barrier(h, h->stream);
+  if (rc) return rc;
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  close_peers(d);
+  if ((rc = rank_barrier(h, h->stream))) return rc;
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  if (d->sym) cudaFree(d->sym);
+  d->sym = nullptr;
+  d->sym_bytes = 0;
+  if (cudaMalloc(&d->sym, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(h, KREA_CUDA_E_NOMEM, "sequence-parallel workspace: cannot allocate %zu bytes", bytes);
+  }
+  d->sym_bytes = bytes;
+  cudaIpcMemHandle_t mine, all[8];
+  CUDA_TRY(h, cudaIpcGetMemHandle(&mine, d->sym));
+  CUDA_TRY(h, cudaMemcpyAsync(d->xchg + d->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice, h->stream));
+  NCCL_TRY(h, d, d->api->AllGather(d->xchg + d->rank * sizeof(mine), d->xchg, sizeof(mine), ncclInt8, d->comm, h->stream));
+  CUDA_TRY(h, cudaMemcpyAsync(all, d->xchg, sizeof(mine) * d->nranks, cudaMemcpyDeviceToHost, h->stream));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  float ok = 1.f;
+  for (int r = 0; r < d->nranks; r++) {
+    if (r == d->rank) {
+      d->peer[r] = d->sym;
+    } else if (cudaIpcOpenMemHandle(&d->peer[r], all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      d->peer[r] = nullptr;
+      ok = 0.f;
+    }
+  }
+  // every rank must take the same path afterwards: agree on the minimum
+  float* w = (float*)(d->xchg + 8 * sizeof(cudaIpcMemHandle_t));
+  CUDA_TRY(h, cudaMemcpyAsync(w, &ok, sizeof(ok), cudaMemcpyHostToDevice, h->stream));
+  if ((rc = rank_barrier(h, h->stream, ncclMin))) return rc;
+  CUDA_TRY(h, cudaMemcpyAsync(&ok, w, sizeof(ok), cudaMemcpyDeviceToHost, h->stream));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  if (ok < 0.5f) {
+    close_peers(d);
+    d->p2p = false;
+  }
+  return KREA_CUDA_OK;
+}
+
 static int validate_a2a(krea_cuda* h, const krea_cuda_a2a_args* a, bool to_heads) {
   if (!a) return fail(h, KREA_CUDA_E_ARG, "reshard: null arguments");
   if (a->rows_local < 0 || a->cols_per_rank < 0) return fail(h, KREA_CUDA_E_ARG, "reshard: negative size");
@@ -188,8 +270,11 @@ void krea_dist_release(krea_cuda* h) {
   KreaDist* d = h ? h->dist : nullptr;
   if (!d) return;
   if (d->side) cudaStreamSynchronize(d->side);
+  close_peers(d);
   if (d->comm) d->api->CommDestroy(d->comm);
   if (d->ws) cudaFree(d->ws);
+  if (d->sym) cudaFree(d->sym);
+  if (d->xchg) cudaFree(d->xchg);
   for (cudaEvent_t e : d->ev)
     if (e) cudaEventDestroy(e);
   if (d->side) cudaStreamDestroy(d->side);
@@ -249,8 +334,26 @@ int krea_cuda_dist_init(krea_cuda* h, int rank, int nranks, const void* id) {
   }
   d->rank = rank;
   d->nranks = nranks;
+  // exchange mode: peer stores unless the environment asks for NCCL transfers, the group is too large for
+  // the kernels' tables, or a first small mapping round fails on any rank
+  const char* mode = getenv("KREA_CUDA_SEQPAR_EXCHANGE");
+  d->p2p = nranks >= 2 && nranks <= 8 && !(mode && strcmp(mode, "nccl") == 0);
+  if (cudaMalloc((void**)&d->xchg, XCHG_BYTES) != cudaSuccess || cudaMemset(d->xchg, 0, XCHG_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    krea_dist_release(h);
+    return fail(h, KREA_CUDA_E_NOMEM, "dist_init: cannot allocate the exchange scratch");
+  }
+  if (d->p2p) {
+    const int rc = sym_alloc(h, 1 << 20);
+    if (rc) {
+      krea_dist_release(h);
+      return rc;
+    }
+  }
   return KREA_CUDA_OK;
 }
+
+int krea_cuda_dist_exchange_mode(krea_cuda* h) { return (h && h->dist && h->dist->comm) ? (h->dist->p2p ? 1 : 0) : -1; }
 
 int krea_cuda_dist_rank(krea_cuda* h) { return (h && h->dist && h->dist->comm) ? h->dist->rank : -1; }
 int krea_cuda_dist_size(krea_cuda* h) { return (h && h->dist && h->dist->comm) ? h->dist->nranks : 0; }
@@ -359,6 +462,52 @@ int krea_cuda_seqpar_joint_attention(krea_cuda* h, const krea_cuda_seqpar_args* 
 
   CUDA_TRY(h, cudaSetDevice(h->device));
   const size_t q_bytes = round256((size_t)a->seq * cl * 2), kv_bytes = round256((size_t)a->seq * kcl * 2);
+  if (d->p2p) {
+    // ---- peer stores: no staging copies, no NCCL transfers ----
+    // symmetric layout (same offsets on every rank): Q by heads | K | V | output by rows | normalised K (local use)
+    const size_t o_bytes = round256((size_t)rl * a->heads * 128 * 2);
+    const size_t need = q_bytes + 2 * kv_bytes + o_bytes + kv_bytes;
+    if (d->sym_bytes < need && (rc = sym_alloc(h, need))) return rc;
+  }
+  if (d->p2p) {
+    const size_t o_bytes = round256((size_t)rl * a->heads * 128 * 2);
+    const size_t off_q = 0, off_k = q_bytes, off_v = q_bytes + kv_bytes, off_o = q_bytes + 2 * kv_bytes, off_kn = off_o + o_bytes;
+    char* w = (char*)d->sym;
+    j.Q = w + off_q; j.K = w + off_k; j.V = w + off_v;
+    j.ldo = a->heads * 128;                  // the scattered output rows are full rows of all heads
+    j.O = w + off_o;                          // (placeholder for validation; the kernel uses the block table)
+    if ((rc = krea_validate_joint(h, &j))) return rc;
+    // 1. every rank stores its rows of the head blocks straight into their owners' Q / K / V
+    const void* srcs[3] = {a->K, a->V, a->Q};
+    const int lds[3] = {a->ldk, a->ldv, a->ldq};
+    const size_t offs[3] = {off_k, off_v, off_q};
+    const int cols[3] = {kcl, kcl, cl};
+    for (int t = 0; t < 3; t++) {
+      ReshardParams p{};
+      p.src = (const __nv_bfloat16*)srcs[t];
+      p.dst = (__nv_bfloat16*)(w + offs[t]);
+      for (int r = 0; r < 8; r++) p.dst_peer[r] = (__nv_bfloat16*)((char*)d->peer[r < P ? r : P - 1] + offs[t]);
+      p.dst_row0 = d->rank * rl;
+      p.nranks = P;
+      p.rows = rl;
+      p.cols_per_rank = cols[t];
+      p.src_ld = lds[t];
+      CUDA_TRY(h, launch_reshard_pack(p, h->stream));
+      h->launches++;
+    }
+    // 2. all rows of my heads have landed once every rank has passed this point
+    if ((rc = rank_barrier(h, h->stream))) return rc;
+    if ((rc = krea_joint_prepass(h, &j, w + off_kn))) return rc;
+    // 3. attention; the epilogue stores each query row into its home rank's output rows, at my heads' columns
+    void* o_blk[8];
+    for (int r = 0; r < P; r++) o_blk[r] = (char*)d->peer[r] + off_o + (size_t)d->rank * cl * 2;
+    if ((rc = krea_joint_attend_scatter(h, &j, w + off_kn, o_blk, P, rl))) return rc;
+    // 4. my output rows are complete once every rank's attention kernel has finished
+    if ((rc = rank_barrier(h, h->stream))) return rc;
+    CUDA_TRY(h, cudaMemcpy2DAsync(a->O, (size_t)a->ldo * 2, w + off_o, (size_t)a->heads * 128 * 2, (size_t)a->heads * 128 * 2, rl,
+                                  cudaMemcpyDeviceToDevice, h->stream));
+    return KREA_CUDA_OK;
+  }
   void* base = nullptr;
   // send stage | Q (reused for the returning output blocks) | output by heads | K | V | normalised K
   if ((rc = dist_ws(h, 3 * q_bytes + 3 * kv_bytes, &base))) return rc;

@@ -66,6 +66,8 @@ static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; 
 // the fused call in two steps: K normalisation pass (+ logit bound), then the attention kernel
 int krea_joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch);
 int krea_joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch);
+// ... with output row r stored under o_blk[r / rows] (n bases, possibly in other GPUs' memory) instead of a->O
+int krea_joint_attend_scatter(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch, void* const* o_blk, int n, int rows);
 int krea_validate_joint(krea_cuda* h, const krea_cuda_joint_args* a);
 // Implemented in dist_nccl.cu: releases the communicator and its workspace (called by krea_cuda_destroy).
 void krea_dist_release(krea_cuda* h);

@@ -263,6 +263,8 @@ struct AttnCall {
   const float* logit_bound;
   int causal, q_pos0;
   const float *QB, *KB;
+  void* const* o_blk;   // row-block scatter of the output (see AttnParams::O_blk), nullptr = none
+  int o_blk_n, o_blk_rows;
 };
 
 static int run_attention(krea_cuda* h, const AttnCall& c) {
@@ -298,6 +300,15 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
   p.logit_bound = (h->static_bound && c.wq) ? c.logit_bound : nullptr;
   p.status = h->status_dev;
+  if (c.o_blk != nullptr) {
+    if (c.batch != 1 || c.o_blk_rows <= 0 || c.o_blk_n < 1 || c.o_blk_n > 8 || (int64_t)c.o_blk_n * c.o_blk_rows < c.Lq)
+      return fail(h, KREA_CUDA_E_ARG, "attention: bad output row-block table");
+    for (int k = 0; k < 8; k++) {
+      p.O_blk[k] = (__nv_bfloat16*)c.o_blk[k < c.o_blk_n ? k : c.o_blk_n - 1];
+      if (!p.O_blk[k] || !aligned16(p.O_blk[k])) return fail(h, KREA_CUDA_E_ARG, "attention: null or misaligned output block");
+    }
+    p.o_blk_rows = c.o_blk_rows;
+  }
 
   CUtensorMap tmK, tmV;
   memset(&tmK, 0, sizeof(tmK));
@@ -381,7 +392,8 @@ static int joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr
   return KREA_CUDA_OK;
 }
 
-static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr, void* const* o_blk = nullptr, int o_blk_n = 0,
+                        int o_blk_rows = 0) {
   const int batch = a->batch <= 0 ? 1 : a->batch;
   const int kvheads = a->heads / a->group;
   AttnCall c{};
@@ -393,6 +405,7 @@ static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr)
   c.wq = a->wq; c.cos = a->cos; c.sin = a->sin; c.eps = a->eps; c.rope_mode = a->rope_mode; c.q_row0 = a->q_row0;
   c.text_len = a->text_len; c.text_slots = a->text_slots;
   c.logit_bound = (float*)(h->status_dev + 8);
+  c.o_blk = o_blk; c.o_blk_n = o_blk_n; c.o_blk_rows = o_blk_rows;
   return run_attention(h, c);
 }
 
@@ -752,4 +765,7 @@ int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard_args* a) { re
 
 int krea_joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch) { return joint_prepass(h, a, k_scratch); }
 int krea_joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch) { return joint_attend(h, a, k_scratch); }
+int krea_joint_attend_scatter(krea_cuda* h, const krea_cuda_joint_args* a, void* k_scratch, void* const* o_blk, int n, int rows) {
+  return joint_attend(h, a, k_scratch, o_blk, n, rows);
+}
 int krea_validate_joint(krea_cuda* h, const krea_cuda_joint_args* a) { return validate_joint(h, a); }

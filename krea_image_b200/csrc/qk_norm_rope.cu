@@ -172,7 +172,14 @@ __global__ void __launch_bounds__(256) reshard_kernel(const ReshardParams p, int
     const int peer = (int)(t / p.rows);
     if (!unpack) {
       const uint4 x = __ldg((const uint4*)(p.src + (size_t)row * p.src_ld + p.src_col0 + (size_t)peer * p.cols_per_rank) + v);
-      *((uint4*)(p.dst + ((size_t)peer * p.rows + row) * p.cols_per_rank) + v) = x;
+      if (p.dst_peer[0] != nullptr) {
+        __nv_bfloat16* base = p.dst_peer[0];   // parameter space wants compile-time indices: selects
+#pragma unroll
+        for (int k = 1; k < 8; k++) base = peer == k ? p.dst_peer[k] : base;
+        *((uint4*)(base + ((size_t)p.dst_row0 + row) * p.cols_per_rank) + v) = x;
+      } else {
+        *((uint4*)(p.dst + ((size_t)peer * p.rows + row) * p.cols_per_rank) + v) = x;
+      }
     } else {
       const uint4 x = __ldg((const uint4*)(p.src + ((size_t)peer * p.rows + row) * p.cols_per_rank) + v);
       *((uint4*)(p.dst + (size_t)row * p.dst_ld + p.dst_col0 + (size_t)peer * p.cols_per_rank) + v) = x;

@@ -170,6 +170,10 @@ class KreaCuda:
         buf = ctypes.create_string_buffer(uid, B.DIST_ID_BYTES)
         self._check(self.lib.krea_cuda_dist_init(self.h, rank, nranks, ctypes.cast(buf, ctypes.c_void_p)))
 
+    def dist_exchange_mode(self) -> str:
+        """'p2p' (peer stores over NVLink, NCCL only for barriers), 'nccl' (ncclSend/ncclRecv) or 'none'."""
+        return {1: "p2p", 0: "nccl"}.get(int(self.lib.krea_cuda_dist_exchange_mode(self.h)), "none")
+
     def dist_rank(self) -> int:
         return int(self.lib.krea_cuda_dist_rank(self.h))
 

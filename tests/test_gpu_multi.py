@@ -80,16 +80,24 @@ def _worker(rank, world, port, out_dir):
         assert rel <= 5e-3 and np.abs(got - ref).max() <= 2e-2, f"ulysses rank {rank}: {rel}"
         assert torch.equal(out.view(torch.int16), o_all[lo:hi].contiguous().view(torch.int16))   # same kernels, same bits
 
-        # ---- the same through the library's own NCCL communicator: one C call per step ----
-        assert kc.dist_size() == 0 and kc.dist_rank() == -1
-        assert kd.init_native(kc) == (rank, world)
-        assert kc.dist_size() == world and kc.dist_rank() == rank
-        na = kd.NativeUlyssesAttention(kc, plan)
+        # ---- the same through the library's own communicator: one C call per step, first with peer
+        # stores (pack kernels and the attention epilogue write into the other GPU's memory, NCCL only
+        # for barriers), then with NCCL transfers ----
         xl = x[lo:hi].contiguous()
-        for _ in range(2):   # the second call reuses the workspace
-            out2 = na(xl, d_wq, d_wk, d_cos, d_sin)
-            kc.dist_sync(60000)
-            assert torch.equal(out2.view(torch.int16), out.view(torch.int16))
+        assert kc.dist_size() == 0 and kc.dist_rank() == -1 and kc.dist_exchange_mode() == "none"
+        for mode in ("p2p", "nccl"):
+            os.environ["KREA_CUDA_SEQPAR_EXCHANGE"] = mode
+            assert kd.init_native(kc) == (rank, world)
+            assert kc.dist_size() == world and kc.dist_rank() == rank
+            assert kc.dist_exchange_mode() == mode, kc.dist_exchange_mode()
+            na = kd.NativeUlyssesAttention(kc, plan)
+            for _ in range(3):   # later calls reuse the workspace
+                out2 = na(xl, d_wq, d_wk, d_cos, d_sin)
+                kc.dist_sync(60000)
+                assert torch.equal(out2.view(torch.int16), out.view(torch.int16)), mode
+                out2.zero_()
+            if mode == "p2p":
+                kc.dist_shutdown()
         # the two exchanges on their own: there and back again
         rl, cl = plan.rows_local, plan.cols_local
         q_heads = torch.zeros((S, cl), dtype=torch.bfloat16, device="cuda")

@@ -68,8 +68,9 @@ KREA_CUDA_API uint64_t krea_cuda_launch_count(krea_cuda* h);
 /* Per-operator GPU timing, the counterpart of the reference's KREA_PROFILE marks (Metal::mark,
  * engine/src/metal.h:126-145): while enabled, every kernel launch is bracketed by CUDA events on the
  * stream.  krea_cuda_profile_read synchronises the stream and returns the accumulated device time and
- * launch count of the prologue kernel (which = 0) or the attention kernel (which = 1) since the last
- * krea_cuda_profile_enable(h, 1), then clears them. */
+ * launch count of the prologue kernel (which = 0), the attention kernel (which = 1), the exchange
+ * kernels and copies of the sequence-parallel step (which = 2) or its rank barriers (which = 3) since the
+ * last krea_cuda_profile_enable(h, 1), then clears them. */
 KREA_CUDA_API int krea_cuda_profile_enable(krea_cuda* h, int on);
 KREA_CUDA_API int krea_cuda_profile_read(krea_cuda* h, int which, double* total_ms, int* launches);
 

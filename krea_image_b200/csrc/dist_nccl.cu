@@ -492,18 +492,26 @@ int krea_cuda_seqpar_joint_attention(krea_cuda* h, const krea_cuda_seqpar_args* 
       p.rows = rl;
       p.cols_per_rank = cols[t];
       p.src_ld = lds[t];
+      ProfileMark pm(h, 2);
       CUDA_TRY(h, launch_reshard_pack(p, h->stream));
       h->launches++;
     }
     // 2. all rows of my heads have landed once every rank has passed this point
-    if ((rc = rank_barrier(h, h->stream))) return rc;
+    {
+      ProfileMark pm(h, 3);
+      if ((rc = rank_barrier(h, h->stream))) return rc;
+    }
     if ((rc = krea_joint_prepass(h, &j, w + off_kn))) return rc;
     // 3. attention; the epilogue stores each query row into its home rank's output rows, at my heads' columns
     void* o_blk[8];
     for (int r = 0; r < P; r++) o_blk[r] = (char*)d->peer[r] + off_o + (size_t)d->rank * cl * 2;
     if ((rc = krea_joint_attend_scatter(h, &j, w + off_kn, o_blk, P, rl))) return rc;
     // 4. my output rows are complete once every rank's attention kernel has finished
-    if ((rc = rank_barrier(h, h->stream))) return rc;
+    {
+      ProfileMark pm(h, 3);
+      if ((rc = rank_barrier(h, h->stream))) return rc;
+    }
+    ProfileMark pm(h, 2);
     CUDA_TRY(h, cudaMemcpy2DAsync(a->O, (size_t)a->ldo * 2, w + off_o, (size_t)a->heads * 128 * 2, (size_t)a->heads * 128 * 2, rl,
                                   cudaMemcpyDeviceToDevice, h->stream));
     return KREA_CUDA_OK;
@@ -534,6 +542,7 @@ int krea_cuda_seqpar_joint_attention(krea_cuda* h, const krea_cuda_seqpar_args* 
   CUDA_TRY(h, cudaStreamWaitEvent(h->stream, d->ev[2], 0));
   if ((rc = krea_joint_attend(h, &j, kn))) return rc;
   // the output goes home on the main stream; its blocks are received over the (now dead) Q rows
+  ProfileMark pm(h, 2);
   return heads_to_seq_on(h, oh, a->O, qh, rl, cl, a->ldo, 0, h->stream);
 }
 

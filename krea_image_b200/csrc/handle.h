@@ -39,7 +39,7 @@ struct krea_cuda {
   void* bounce = nullptr;           // pinned host staging for the small operands of the host entry point
   size_t bounce_bytes = 0;
   bool profiling = false;
-  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[2];   // pending (start, stop) pairs per kernel kind
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[4];   // pending (start, stop) pairs per kind of work
   std::vector<cudaEvent_t> event_pool;
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
 };
@@ -61,6 +61,35 @@ static inline int fail(krea_cuda* h, int code, const char* fmt, ...) {
 
 static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
+
+// Brackets one kernel launch with events while profiling is on (kind 0 = prologue,
+// 1 = attention, 2 = exchange kernels and copies of the sequence-parallel step, 3 = its rank barriers).
+struct ProfileMark {
+  krea_cuda* h;
+  int kind;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  static cudaEvent_t get(krea_cuda* h) {
+    if (!h->event_pool.empty()) {
+      cudaEvent_t e = h->event_pool.back();
+      h->event_pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+  ProfileMark(krea_cuda* h_, int kind_) : h(h_), kind(kind_) {
+    if (!h->profiling) return;
+    e0 = get(h);
+    e1 = get(h);
+    if (e0) cudaEventRecord(e0, h->stream);
+  }
+  ~ProfileMark() {
+    if (!e0 || !e1) return;
+    cudaEventRecord(e1, h->stream);
+    h->marks[kind].push_back({e0, e1});
+  }
+};
 
 // Implemented in krea_cuda.cu for the other source files of the library.
 // the fused call in two steps: K normalisation pass (+ logit bound), then the attention kernel

@@ -21,34 +21,6 @@
 
 using namespace krea;
 
-// Brackets one kernel launch with events while profiling is on (kind 0 = prologue, 1 = attention).
-struct ProfileMark {
-  krea_cuda* h;
-  int kind;
-  cudaEvent_t e0 = nullptr, e1 = nullptr;
-  static cudaEvent_t get(krea_cuda* h) {
-    if (!h->event_pool.empty()) {
-      cudaEvent_t e = h->event_pool.back();
-      h->event_pool.pop_back();
-      return e;
-    }
-    cudaEvent_t e = nullptr;
-    cudaEventCreate(&e);
-    return e;
-  }
-  ProfileMark(krea_cuda* h_, int kind_) : h(h_), kind(kind_) {
-    if (!h->profiling) return;
-    e0 = get(h);
-    e1 = get(h);
-    if (e0) cudaEventRecord(e0, h->stream);
-  }
-  ~ProfileMark() {
-    if (!e0 || !e1) return;
-    cudaEventRecord(e1, h->stream);
-    h->marks[kind].push_back({e0, e1});
-  }
-};
-
 extern "C" {
 
 krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
@@ -115,7 +87,7 @@ void krea_cuda_destroy(krea_cuda* h) {
   if (h->ws) cudaFree(h->ws);
   for (int i = 0; i < 8; i++)
     if (h->stage[i]) cudaFree(h->stage[i]);
-  for (int k = 0; k < 2; k++)
+  for (int k = 0; k < 4; k++)
     for (auto& m : h->marks[k]) {
       cudaEventDestroy(m.first);
       cudaEventDestroy(m.second);
@@ -144,7 +116,7 @@ int krea_cuda_profile_enable(krea_cuda* h, int on) {
   if (!h) return KREA_CUDA_E_ARG;
   CUDA_TRY(h, cudaSetDevice(h->device));
   CUDA_TRY(h, cudaStreamSynchronize(h->stream));
-  for (int k = 0; k < 2; k++) {
+  for (int k = 0; k < 4; k++) {
     for (auto& m : h->marks[k]) {
       h->event_pool.push_back(m.first);
       h->event_pool.push_back(m.second);
@@ -156,7 +128,7 @@ int krea_cuda_profile_enable(krea_cuda* h, int on) {
 }
 
 int krea_cuda_profile_read(krea_cuda* h, int which, double* total_ms, int* launches) {
-  if (!h || which < 0 || which > 1 || !total_ms || !launches) return fail(h, KREA_CUDA_E_ARG, "profile_read: bad arguments");
+  if (!h || which < 0 || which > 3 || !total_ms || !launches) return fail(h, KREA_CUDA_E_ARG, "profile_read: bad arguments");
   CUDA_TRY(h, cudaSetDevice(h->device));
   CUDA_TRY(h, cudaStreamSynchronize(h->stream));
   double sum = 0.0;

@@ -211,6 +211,37 @@ typedef struct {
 } krea_cuda_layerwise_args;
 KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwise_args* a);
 
+/* ---- `.qw` weight files (the reference's WeightFile, engine/src/weights.h:26-75, weights.mm:16-81; format
+ * written by tools/convert.py:49-89) ----
+ * The on-disk format that supplies the path's QK-norm weights `L<l>.qn` / `L<l>.kn` (f32[128]):
+ * "QWTS", u32 version, u64 header length, JSON header {"tensors": {name: {dtype, shape, offset, nbytes}},
+ * "meta": {...}}, data section at the next multiple of 16 KiB.  dtype is one of "bf16", "f16", "f32", "i8".
+ * The file is mapped read-only; queries need no GPU.  krea_cuda_qw_upload copies a byte range of the data
+ * section to device memory on the handle's stream (staged through pinned memory) and returns when the
+ * bytes are on the device.  Strings returned here live as long as the file object. */
+typedef struct krea_qw krea_qw;
+typedef struct {
+  const char* name;
+  const char* dtype;
+  int rank;
+  int64_t shape[8];
+  uint64_t offset;   /* relative to the data section (TensorInfo::offset) */
+  uint64_t nbytes;
+} krea_cuda_qw_info;
+KREA_CUDA_API krea_qw* krea_cuda_qw_open(const char* path, char* err, int errlen);   /* WeightFile::WeightFile */
+KREA_CUDA_API void krea_cuda_qw_close(krea_qw* q);
+KREA_CUDA_API int krea_cuda_qw_count(const krea_qw* q);
+KREA_CUDA_API int krea_cuda_qw_info_at(const krea_qw* q, int index, krea_cuda_qw_info* out);       /* sorted by name */
+KREA_CUDA_API int krea_cuda_qw_find(const krea_qw* q, const char* name, krea_cuda_qw_info* out);   /* WeightFile::info / has */
+KREA_CUDA_API const void* krea_cuda_qw_host_ptr(const krea_qw* q, uint64_t offset);                /* WeightFile::host_ptr */
+KREA_CUDA_API const char* krea_cuda_qw_meta(const krea_qw* q);                                     /* WeightFile::meta_json */
+KREA_CUDA_API uint64_t krea_cuda_qw_data_bytes(const krea_qw* q);
+KREA_CUDA_API int krea_cuda_qw_span(const krea_qw* q, const char* prefix, uint64_t* off, uint64_t* len); /* WeightFile::span */
+KREA_CUDA_API int krea_cuda_qw_upload(krea_cuda* h, const krea_qw* q, uint64_t off, uint64_t len, void* dst_device);
+/* The head dimension whose |qn[d]*kn[d]| is the largest one above gain_threshold (the reference uses 256), or
+ * -1: the dimension DiT::DiT routes through the fp32 side buffers (engine/src/model.mm:226-239). */
+KREA_CUDA_API int krea_cuda_qw_big_dim(const float* qn, const float* kn, float gain_threshold);
+
 /* ---- sequence-parallel resharding helpers (no counterpart in the reference, which is single-device) ----
  * Pack / unpack kernels either side of an all-to-all that turns sequence-sharded rows (all heads, rows
  * [r*S/P, (r+1)*S/P)) into head-sharded rows (all S rows, heads [r*H/P, (r+1)*H/P)) and back.

@@ -55,6 +55,11 @@ class LayerwiseArgs(ctypes.Structure):
                 ("q_off", _int), ("k_off", _int), ("v_off", _int), ("g_off", _int)]
 
 
+class QwInfo(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("dtype", ctypes.c_char_p), ("rank", _int), ("shape", _i64 * 8),
+                ("offset", ctypes.c_uint64), ("nbytes", ctypes.c_uint64)]
+
+
 class A2AArgs(ctypes.Structure):
     _fields_ = [("src", _vp), ("dst", _vp), ("rows_local", _int), ("cols_per_rank", _int),
                 ("src_ld", _int), ("dst_ld", _int), ("src_col0", _int), ("dst_col0", _int)]
@@ -86,6 +91,17 @@ SYMBOLS = {
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
     "krea_cuda_layerwise_attn": (_int, [_vp, ctypes.POINTER(LayerwiseArgs)]),
+    "krea_cuda_qw_open": (_vp, [ctypes.c_char_p, ctypes.c_char_p, _int]),
+    "krea_cuda_qw_close": (None, [_vp]),
+    "krea_cuda_qw_count": (_int, [_vp]),
+    "krea_cuda_qw_info_at": (_int, [_vp, _int, ctypes.POINTER(QwInfo)]),
+    "krea_cuda_qw_find": (_int, [_vp, ctypes.c_char_p, ctypes.POINTER(QwInfo)]),
+    "krea_cuda_qw_host_ptr": (_vp, [_vp, ctypes.c_uint64]),
+    "krea_cuda_qw_meta": (ctypes.c_char_p, [_vp]),
+    "krea_cuda_qw_data_bytes": (ctypes.c_uint64, [_vp]),
+    "krea_cuda_qw_span": (_int, [_vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]),
+    "krea_cuda_qw_upload": (_int, [_vp, _vp, ctypes.c_uint64, ctypes.c_uint64, _vp]),
+    "krea_cuda_qw_big_dim": (_int, [_vp, _vp, ctypes.c_float]),
     "krea_cuda_reshard_pack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_reshard_unpack": (_int, [_vp, ctypes.POINTER(ReshardArgs)]),
     "krea_cuda_dist_unique_id": (_int, [_vp, ctypes.c_char_p, _int]),

@@ -96,6 +96,7 @@ void krea_cuda_destroy(krea_cuda* h) {
   for (int i = 0; i < 18; i++)
     if (h->pipe_ev[i]) cudaEventDestroy(h->pipe_ev[i]);
   if (h->bounce) cudaFreeHost(h->bounce);
+  if (h->qw_stage) cudaFreeHost(h->qw_stage);
   if (h->copy_in) cudaStreamDestroy(h->copy_in);
   if (h->copy_out) cudaStreamDestroy(h->copy_out);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);

@@ -1,0 +1,106 @@
+"""`.qw` weight files through libkrea_cuda's reader (the reference's WeightFile, engine/src/weights.h:26-75).
+
+The file is mapped by the library; tensors come back as numpy views of that mapping (no copy) and byte
+ranges can be uploaded to device memory through a KreaCuda handle.  Opening and querying need no GPU.
+"""
+import ctypes
+import json
+
+import numpy as np
+
+from . import binding as B
+from .ops import KreaCudaError, _ptr
+
+_NP = {"f32": np.float32, "f16": np.float16, "i8": np.int8, "bf16": np.uint16}   # bf16 as raw bits
+
+
+class TensorInfo:
+    def __init__(self, info: B.QwInfo):
+        self.name = info.name.decode()
+        self.dtype = info.dtype.decode()
+        self.shape = tuple(int(info.shape[i]) for i in range(info.rank))
+        self.offset = int(info.offset)
+        self.nbytes = int(info.nbytes)
+
+    def __repr__(self):
+        return f"TensorInfo({self.name!r}, {self.dtype}, {self.shape}, offset={self.offset}, nbytes={self.nbytes})"
+
+
+class WeightFile:
+    def __init__(self, path: str):
+        self.lib = B.load()
+        err = ctypes.create_string_buffer(512)
+        self.q = self.lib.krea_cuda_qw_open(str(path).encode(), err, 512)
+        if not self.q:
+            raise KreaCudaError(B.E_ARG, err.value.decode())
+        self.path = str(path)
+
+    def close(self):
+        if self.q:
+            self.lib.krea_cuda_qw_close(self.q)
+            self.q = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __len__(self):
+        return int(self.lib.krea_cuda_qw_count(self.q))
+
+    def names(self):
+        out, info = [], B.QwInfo()
+        for i in range(len(self)):
+            self.lib.krea_cuda_qw_info_at(self.q, i, ctypes.byref(info))
+            out.append(info.name.decode())
+        return out
+
+    def has(self, name: str) -> bool:
+        return self.lib.krea_cuda_qw_find(self.q, name.encode(), None) == B.OK
+
+    def info(self, name: str) -> TensorInfo:
+        info = B.QwInfo()
+        if self.lib.krea_cuda_qw_find(self.q, name.encode(), ctypes.byref(info)) != B.OK:
+            raise KeyError(f"missing tensor: {name} in {self.path}")    # weights.mm:88
+        return TensorInfo(info)
+
+    def get(self, name: str) -> np.ndarray:
+        """numpy view of the mapping (read-only; bf16 tensors as uint16 bits).  Valid until close()."""
+        ti = self.info(name)
+        addr = self.lib.krea_cuda_qw_host_ptr(self.q, ti.offset)
+        buf = (ctypes.c_char * ti.nbytes).from_address(addr)
+        a = np.frombuffer(buf, dtype=_NP[ti.dtype]).reshape(ti.shape)
+        a.flags.writeable = False
+        return a
+
+    def meta(self) -> dict:
+        m = self.lib.krea_cuda_qw_meta(self.q).decode()
+        return json.loads(m) if m else {}
+
+    def data_bytes(self) -> int:
+        return int(self.lib.krea_cuda_qw_data_bytes(self.q))
+
+    def span(self, prefix: str):
+        """(offset, length) of the data-section range covering every tensor whose name starts with prefix."""
+        off, ln = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        if self.lib.krea_cuda_qw_span(self.q, prefix.encode(), ctypes.byref(off), ctypes.byref(ln)) != B.OK:
+            raise KeyError(f"no tensor of {self.path} starts with {prefix!r}")
+        return int(off.value), int(ln.value)
+
+    def upload(self, kc, off: int, length: int, dst):
+        """Copies data-section bytes [off, off+length) to the device tensor / pointer dst."""
+        kc._check(self.lib.krea_cuda_qw_upload(kc.h, self.q, off, length, _ptr(dst)))
+
+    def upload_tensor(self, kc, name: str, dst):
+        ti = self.info(name)
+        self.upload(kc, ti.offset, ti.nbytes, dst)
+        return ti
+
+
+def big_dim(qn: np.ndarray, kn: np.ndarray, gain_threshold: float = 256.0) -> int:
+    """The head dimension the reference routes through fp32 side buffers (model.mm:226-239), or -1."""
+    qn = np.ascontiguousarray(qn, dtype=np.float32)
+    kn = np.ascontiguousarray(kn, dtype=np.float32)
+    assert qn.size == 128 and kn.size == 128
+    return int(B.load().krea_cuda_qw_big_dim(qn.ctypes.data, kn.ctypes.data, ctypes.c_float(gain_threshold)))

@@ -317,7 +317,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       float m_i = -INFINITY;   // running max, log2 units (scaled scores)
       float l_i = 0.f;         // running row sum of exp2(s - m), fp32
       const float sc2 = p.scale_log2;
-      const float bound = p.logit_bound != nullptr ? __ldg(p.logit_bound) : INFINITY;
+      griddep_wait();          // the logit bound is written by the kernel before this one
+      const float bound = p.logit_bound != nullptr ? *(const volatile float*)p.logit_bound : INFINITY;
       // EXTRA: the rarely used score modifiers (causal mask, fp32 rank-1 term) are compiled into a variant
       // of their own so that the common loop does not carry their registers and instructions.
       auto softmax_tiles = [&](auto bounded_tag, auto extra_tag) {
@@ -532,6 +533,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (lane == 0 && n_tiles > 0) {
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
+      griddep_wait();          // K comes from the kernel before this one (the normalisation pre-pass)
       int issued = 0;
       for (int j = 0; j < n_tiles; j++) {
         const int key0 = tile_of(j) * BN;
@@ -684,9 +686,17 @@ static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, c
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
-  attn_fwd_sm100<SPLIT, EMU><<<grid, Cfg<SPLIT>::THREADS, smem, stream>>>(tmK, tmV, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
+  cfg.blockDim = dim3(Cfg<SPLIT>::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, attn_fwd_sm100<SPLIT, EMU>, tmK, tmV, p);
 }
 
 cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, int split, int emu, cudaStream_t stream) {

@@ -39,6 +39,11 @@ struct AttnParams {
   // The bases may point into other GPUs' memory (plain peer stores); batch must be 1.
   __nv_bfloat16* O_blk[8];
   int o_blk_rows;
+  // 1: launch with programmatic stream serialisation, so that barrier set-up, TMEM allocation and Q staging
+  // overlap the tail of the previous kernel in the stream (the K pre-pass).  Only for callers whose Q,
+  // tables and weights do not come from that previous kernel: K, V and the logit bound are read after
+  // griddepcontrol.wait, everything else before it.
+  int pdl;
   uint32_t* status;            // device word: 0 = ok, else (site | qblk << 8 | head << 20) of a timed-out wait
   long long* trace;            // tuning builds only (KREA_ATTN_TRACE): clock64 samples of CTA 0, else nullptr
 };
@@ -67,6 +72,7 @@ struct NormRopeParams {
   float* qbig;
   float* kbig;
   // joint call only: the pre-pass also derives the a-priori logit bound from both weight vectors
+  int pdl;                     // 1: launch with programmatic stream serialisation (the kernel waits for its predecessors first thing)
   const float* bound_wq;       // nullptr = do not compute
   float* bound_out;
   float bound_scale_log2;      // softmax scale * log2(e)

@@ -70,6 +70,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     if (v == 1 || v == 2) h->split = v;
   }
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
+  if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);
     if (v >= 0 && v <= 1) h->emu = v;
@@ -236,6 +237,7 @@ struct AttnCall {
   const float* logit_bound;
   int causal, q_pos0;
   const float *QB, *KB;
+  bool pdl;             // programmatic dependent launch after the K pre-pass (fused call only)
   void* const* o_blk;   // row-block scatter of the output (see AttnParams::O_blk), nullptr = none
   int o_blk_n, o_blk_rows;
 };
@@ -273,6 +275,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
   p.logit_bound = (h->static_bound && c.wq) ? c.logit_bound : nullptr;
   p.status = h->status_dev;
+  p.pdl = c.pdl ? 1 : 0;
   if (c.o_blk != nullptr) {
     if (c.batch != 1 || c.o_blk_rows <= 0 || c.o_blk_n < 1 || c.o_blk_n > 8 || (int64_t)c.o_blk_n * c.o_blk_rows < c.Lq)
       return fail(h, KREA_CUDA_E_ARG, "attention: bad output row-block table");
@@ -356,6 +359,7 @@ static int joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr
   n.bound_wq = a->wq;
   n.bound_out = (float*)(h->status_dev + 8);   // a device float next to the status word
   n.bound_scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);
+  n.pdl = h->pdl ? 1 : 0;
   CUDA_TRY(h, cudaSetDevice(h->device));
   {
     ProfileMark pm(h, 0);
@@ -379,6 +383,7 @@ static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr,
   c.text_len = a->text_len; c.text_slots = a->text_slots;
   c.logit_bound = (float*)(h->status_dev + 8);
   c.o_blk = o_blk; c.o_blk_n = o_blk_n; c.o_blk_rows = o_blk_rows;
+  c.pdl = h->pdl;          // the kernel right before this one in the stream is the K pre-pass
   return run_attention(h, c);
 }
 

@@ -264,6 +264,13 @@ __device__ __forceinline__ uint64_t exp2_emulated_x2(uint64_t x2) {
   return pack_f32x2(r0, r1);
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------------
+// griddep_wait: returns once every grid this one depends on has completed and its writes are visible (at
+// once when the kernel was launched without the programmatic attribute).  griddep_launch: lets the next
+// kernel in the stream, if launched with that attribute, start its prologue while this grid still runs.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- small math helpers ----------------------------------------------------------------------------
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

@@ -383,6 +383,28 @@ def test_sequence_parallel_entry_points_on_one_rank(kc):
     assert kc.dist_size() == 0
 
 
+@pytest.mark.parametrize("env", [{"KREA_CUDA_SPLIT": "2"}, {"KREA_CUDA_EMU": "1"}, {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_EMU": "1"},
+                                 {"KREA_CUDA_STATIC_BOUND": "0"}])
+def test_tuning_knob_variants(monkeypatch, env):
+    """The build-time variants a handle can select through its environment (two softmax threads per row,
+    polynomial exp2 for a quarter of the elements, online max instead of the a-priori bound) give the
+    same results within tolerance, including a ragged key tail, GQA and the padding mask."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    k2 = ops.KreaCuda(0)
+    try:
+        k2.set_stream(torch.cuda.current_stream())
+        B, H, T, gh, gw, group = 2, 4, 48, 19, 16, 2
+        S = T + gh * gw
+        qkv, wq, wk, cos, sin = rand_case(17, B, S, H, T, gh, gw, group=group)
+        tl = np.array([48, 9], dtype=np.int32)
+        want = oracle.joint_attention(qkv, B, S, H, wq, wk, cos, sin, text_len=tl, text_slots=T, group=group)
+        got = run_joint(k2, qkv, B, S, H, wq, wk, cos, sin, group=group, text_len=tl, text_slots=T)
+        check(got, want, None, f"variant {env}")
+    finally:
+        k2.close()
+
+
 def test_argument_errors_launch_nothing(kc):
     n0 = kc.launches
     t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")

@@ -219,41 +219,46 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const __nv_bfloat16* qhead = p.Q + (size_t)b * p.bsq + (size_t)h * D + 8 * c;
         constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;          // 32 or 16
         // MODE 0 / 1 / 2: RMSNorm + interleaved-pair / rotate-half / no RoPE; MODE 3: copy as it is.
-        // Eight rows per lane are in flight at a time: all their global loads are issued before any of
-        // them is used, so the staging costs about two memory round trips instead of sixteen.
+        // Rows are taken in batches of four per lane, software-pipelined over two register sets: the
+        // global loads of batch n+1 are in flight while batch n is normalised, so the staging pays one
+        // memory round trip, not one per batch.
         auto stage_q = [&](auto mode_tag) {
           constexpr int MODE = decltype(mode_tag)::value;
+          constexpr int NB = ROWS_PER_WARP / 8;                 // batches of 4 row slots (2 rows per warp step)
           float wv[8];
           if constexpr (MODE != 3) {
             const float4 wa = __ldg((const float4*)p.wq + 2 * c), wb = __ldg((const float4*)p.wq + 2 * c + 1);
             wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
           }
-#pragma unroll 1
-          for (int batch = 0; batch < ROWS_PER_WARP / 16; batch++) {
-            uint4 raw[8];
-            float4 t0[8], t1[8];     // MODE 0: cos, sin of this chunk's 4 pairs; MODE 1: cos (2 x float4 in t0/t1)
-            float4 t2[8], t3[8];     // MODE 1: sin
-            int rr[8];
+          struct Batch {
+            uint4 raw[4];
+            float4 t0[4], t1[4];     // MODE 0: cos, sin of this chunk's 4 pairs; MODE 1: cos (2 x float4)
+            float4 t2[4], t3[4];     // MODE 1: sin
+          };
+          auto row_of = [&](int batch, int i) { return wt * ROWS_PER_WARP + (batch * 4 + i) * 2 + sub; };   // row inside the tile
+          auto load_batch = [&](int batch, Batch& q) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-              rr[i] = wt * ROWS_PER_WARP + (batch * 8 + i) * 2 + sub;  // row inside the tile
-              const int grow = min(q0 + g * BM + rr[i], p.Lq - 1);     // rows past Lq are clamped, never stored
-              raw[i] = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
+            for (int i = 0; i < 4; i++) {
+              const int grow = min(q0 + g * BM + row_of(batch, i), p.Lq - 1);     // rows past Lq are clamped, never stored
+              q.raw[i] = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
               const size_t trow = (size_t)(p.q_row0 + grow) * 64;
               if constexpr (MODE == 0) {
-                t0[i] = __ldg((const float4*)(p.cos + trow) + c);
-                t1[i] = __ldg((const float4*)(p.sin + trow) + c);
+                q.t0[i] = __ldg((const float4*)(p.cos + trow) + c);
+                q.t1[i] = __ldg((const float4*)(p.sin + trow) + c);
               } else if constexpr (MODE == 1) {
                 const int f = (c & 7) * 2;
-                t0[i] = __ldg((const float4*)(p.cos + trow) + f);
-                t1[i] = __ldg((const float4*)(p.cos + trow) + f + 1);
-                t2[i] = __ldg((const float4*)(p.sin + trow) + f);
-                t3[i] = __ldg((const float4*)(p.sin + trow) + f + 1);
+                q.t0[i] = __ldg((const float4*)(p.cos + trow) + f);
+                q.t1[i] = __ldg((const float4*)(p.cos + trow) + f + 1);
+                q.t2[i] = __ldg((const float4*)(p.sin + trow) + f);
+                q.t3[i] = __ldg((const float4*)(p.sin + trow) + f + 1);
               }
             }
+          };
+          auto compute_batch = [&](int batch, const Batch& q) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-              uint4 v = raw[i];
+            for (int i = 0; i < 4; i++) {
+              uint4 v = q.raw[i];
+              const int rr = row_of(batch, i);
               if constexpr (MODE != 3) {
                 const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
                 float y[8], z[8];
@@ -272,7 +277,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 for (int e = 0; e < 8; e++) y[e] *= rrms * wv[e];
                 if constexpr (MODE == 0) {
                   // interleaved pairs (2i, 2i+1) share frequency i (norm.metal:105-113): this chunk holds pairs 4c..4c+3
-                  const float cf[4] = {t0[i].x, t0[i].y, t0[i].z, t0[i].w}, sf[4] = {t1[i].x, t1[i].y, t1[i].z, t1[i].w};
+                  const float cf[4] = {q.t0[i].x, q.t0[i].y, q.t0[i].z, q.t0[i].w}, sf[4] = {q.t1[i].x, q.t1[i].y, q.t1[i].z, q.t1[i].w};
 #pragma unroll
                   for (int e = 0; e < 4; e++) {
                     z[2 * e] = y[2 * e] * cf[e] - y[2 * e + 1] * sf[e];
@@ -280,8 +285,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                   }
                 } else if constexpr (MODE == 1) {
                   // rotate-half: channel i pairs with i + 64 (norm.metal:114-126), held by the lane 8 chunks away
-                  const float cf[8] = {t0[i].x, t0[i].y, t0[i].z, t0[i].w, t1[i].x, t1[i].y, t1[i].z, t1[i].w};
-                  const float sf[8] = {t2[i].x, t2[i].y, t2[i].z, t2[i].w, t3[i].x, t3[i].y, t3[i].z, t3[i].w};
+                  const float cf[8] = {q.t0[i].x, q.t0[i].y, q.t0[i].z, q.t0[i].w, q.t1[i].x, q.t1[i].y, q.t1[i].z, q.t1[i].w};
+                  const float sf[8] = {q.t2[i].x, q.t2[i].y, q.t2[i].z, q.t2[i].w, q.t3[i].x, q.t3[i].y, q.t3[i].z, q.t3[i].w};
                   const float sg = c < 8 ? -1.f : 1.f;
 #pragma unroll
                   for (int e = 0; e < 8; e++) {
@@ -294,9 +299,18 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 }
                 v = make_uint4(pack_bf16x2(z[0], z[1]), pack_bf16x2(z[2], z[3]), pack_bf16x2(z[4], z[5]), pack_bf16x2(z[6], z[7]));
               }
-              uint8_t* dst = q_smem + g * TILE_BYTES + rr[i] * 128 + (c >> 3) * HALF_BYTES + (((c & 7) ^ (rr[i] & 7)) << 4);
+              uint8_t* dst = q_smem + g * TILE_BYTES + rr * 128 + (c >> 3) * HALF_BYTES + (((c & 7) ^ (rr & 7)) << 4);
               *(uint4*)dst = v;
             }
+          };
+          Batch ba, bb;
+          load_batch(0, ba);
+#pragma unroll 1
+          for (int batch = 0; batch < NB; batch += 2) {
+            load_batch(batch + 1, bb);
+            compute_batch(batch, ba);
+            if (batch + 2 < NB) load_batch(batch + 2, ba);
+            compute_batch(batch + 1, bb);
           }
         };
         if (p.wq == nullptr) stage_q(std::integral_constant<int, 3>{});

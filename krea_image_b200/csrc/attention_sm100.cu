@@ -219,9 +219,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const __nv_bfloat16* qhead = p.Q + (size_t)b * p.bsq + (size_t)h * D + 8 * c;
         constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;          // 32 or 16
         // MODE 0 / 1 / 2: RMSNorm + interleaved-pair / rotate-half / no RoPE; MODE 3: copy as it is.
-        // Rows are taken in batches of four per lane, software-pipelined over two register sets: the
-        // global loads of batch n+1 are in flight while batch n is normalised, so the staging pays one
-        // memory round trip, not one per batch.
+        // All of a lane's rows (16, or 8 with two threads per row) are requested from global memory at
+        // once, so the cold-miss latency of Q is paid once; the cos / sin entries (L2 hits, shared by all
+        // heads) follow in batches of four rows, software-pipelined over two register sets.
         auto stage_q = [&](auto mode_tag) {
           constexpr int MODE = decltype(mode_tag)::value;
           constexpr int NB = ROWS_PER_WARP / 8;                 // batches of 4 row slots (2 rows per warp step)
@@ -231,17 +231,18 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w; wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
           }
           struct Batch {
-            uint4 raw[4];
             float4 t0[4], t1[4];     // MODE 0: cos, sin of this chunk's 4 pairs; MODE 1: cos (2 x float4)
             float4 t2[4], t3[4];     // MODE 1: sin
           };
           auto row_of = [&](int batch, int i) { return wt * ROWS_PER_WARP + (batch * 4 + i) * 2 + sub; };   // row inside the tile
+          auto grow_of = [&](int batch, int i) { return min(q0 + g * BM + row_of(batch, i), p.Lq - 1); };    // rows past Lq are clamped, never stored
+          uint4 raw[NB * 4];
+#pragma unroll
+          for (int k = 0; k < NB * 4; k++) raw[k] = __ldg((const uint4*)(qhead + (size_t)grow_of(k >> 2, k & 3) * p.ldq));
           auto load_batch = [&](int batch, Batch& q) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-              const int grow = min(q0 + g * BM + row_of(batch, i), p.Lq - 1);     // rows past Lq are clamped, never stored
-              q.raw[i] = __ldg((const uint4*)(qhead + (size_t)grow * p.ldq));
-              const size_t trow = (size_t)(p.q_row0 + grow) * 64;
+              const size_t trow = (size_t)(p.q_row0 + grow_of(batch, i)) * 64;
               if constexpr (MODE == 0) {
                 q.t0[i] = __ldg((const float4*)(p.cos + trow) + c);
                 q.t1[i] = __ldg((const float4*)(p.sin + trow) + c);
@@ -257,7 +258,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           auto compute_batch = [&](int batch, const Batch& q) {
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-              uint4 v = q.raw[i];
+              uint4 v = raw[batch * 4 + i];
               const int rr = row_of(batch, i);
               if constexpr (MODE != 3) {
                 const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
@@ -305,7 +306,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           };
           Batch ba, bb;
           load_batch(0, ba);
-#pragma unroll 1
+#pragma unroll
           for (int batch = 0; batch < NB; batch += 2) {
             load_batch(batch + 1, bb);
             compute_batch(batch, ba);

@@ -85,6 +85,17 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       : "memory");
 }
 
+// 3-D tile store shared -> global (bulk async-group completion).  Rows / columns outside the tensor map's
+// extents are not written.  c0 * elemsize must be a multiple of 16 bytes; no coordinate may be negative.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"((uint64_t)tmap), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// returns once the bulk stores committed by this thread have finished READING shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // True in exactly one lane of a fully converged warp.  The MMA warp runs its whole loop converged and
 // only predicates the asynchronous instructions on this, so that descriptor arithmetic and barrier
 // polling stay on the warp-uniform datapath instead of a divergent single-lane path.

@@ -7,14 +7,17 @@
 // implementation shares nothing with it:
 //
 //   * one CTA = NQ tiles of 128 query rows of one (sample, head); S = Q K^T and O += P V run on the
-//     tcgen05 tensor cores with both accumulators in tensor memory (TMEM), issued by a single thread;
+//     tcgen05 tensor cores with all accumulators in tensor memory (TMEM): one score tile shared by the
+//     query tiles in turn, P and O per tile; one elected lane of a converged warp issues the MMAs;
 //   * K and V tiles (128 keys x 128) are fetched by TMA into a ring of 128B-swizzled shared-memory
-//     stages by one producer warp; mbarriers carry every hand-off;
+//     stages by one producer warp; mbarriers carry every hand-off, each with a single in-order waiter;
 //   * each of the 128 threads of a softmax warpgroup owns one query row (= one TMEM lane), so row max
-//     and row sum need no shuffles; P is written back to TMEM (aliasing S) as the A operand of P V;
+//     and row sum need no shuffles; P goes back to TMEM (its own columns) as the A operand of P V;
 //   * Q rows are loaded once with 16-byte loads, optionally RMS-normalised and rotated (fp32), rounded
 //     to bf16 and stored in the swizzled layout the MMA wants - the Q half of the prologue costs no
-//     extra pass over memory;
+//     extra pass over memory; with a programmatic launch all of this overlaps the kernel before;
+//   * the output tile is normalised, gated, rounded to bf16, staged in the idle Q buffer and handed to
+//     the TMA unit as tile stores (or copied out row by row when the rows have several base pointers);
 //   * every wait is bounded: on a timeout the CTA records a code in a status word and runs to its
 //     normal exit (TMEM released), so a logic error can never hang the GPU.
 #include <cuda.h>

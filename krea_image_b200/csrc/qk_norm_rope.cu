@@ -17,8 +17,10 @@ namespace krea {
 // channels) each, so a warp load is 512 contiguous bytes.  The row's cos/sin entries and the weights depend
 // only on the lane's channels, not on the head, and are loaded once per unit.
 // MODE is the rope mode as a compile-time constant (dead branches cost registers, and registers decide
-// how many warps cover the memory latency).
-template <int MODE>
+// how many warps cover the memory latency).  KONLY is the shape of the fused call's pre-pass - K heads
+// only, no fp32 side buffer, fewer than 2^31 units - without the per-step query / key selection and with
+// 32-bit unit arithmetic: the kernel is bound by instruction issue, so every instruction off the step counts.
+template <int MODE, bool KONLY>
 __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopeParams p) {
   const int lane = threadIdx.x & 31;
   griddep_wait();      // with a programmatic launch this kernel may start while its predecessor drains
@@ -39,16 +41,17 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
   }
   const int sub = lane >> 4, c = lane & 15;     // which of the two heads of a step, which 8-channel chunk
   const int heads = p.n_q + p.n_k;
-  float wqv[8], wkv[8];
+  // weights of this lane's 8 channels as four packed pairs
+  uint64_t wq2[4], wk2[4];
 #pragma unroll
-  for (int e = 0; e < 8; e++) wqv[e] = wkv[e] = 0.f;
-  if (p.n_q > 0) {
+  for (int e = 0; e < 4; e++) wq2[e] = wk2[e] = pack_f32x2(0.f, 0.f);
+  if (!KONLY && p.n_q > 0) {
     const float4 a = __ldg((const float4*)p.wq + 2 * c), bq = __ldg((const float4*)p.wq + 2 * c + 1);
-    wqv[0] = a.x; wqv[1] = a.y; wqv[2] = a.z; wqv[3] = a.w; wqv[4] = bq.x; wqv[5] = bq.y; wqv[6] = bq.z; wqv[7] = bq.w;
+    wq2[0] = pack_f32x2(a.x, a.y); wq2[1] = pack_f32x2(a.z, a.w); wq2[2] = pack_f32x2(bq.x, bq.y); wq2[3] = pack_f32x2(bq.z, bq.w);
   }
   if (p.n_k > 0) {
     const float4 a = __ldg((const float4*)p.wk + 2 * c), bk = __ldg((const float4*)p.wk + 2 * c + 1);
-    wkv[0] = a.x; wkv[1] = a.y; wkv[2] = a.z; wkv[3] = a.w; wkv[4] = bk.x; wkv[5] = bk.y; wkv[6] = bk.z; wkv[7] = bk.w;
+    wk2[0] = pack_f32x2(a.x, a.y); wk2[1] = pack_f32x2(a.z, a.w); wk2[2] = pack_f32x2(bk.x, bk.y); wk2[3] = pack_f32x2(bk.z, bk.w);
   }
   // work unit = (row, batch of up to eight heads): short dependent chains (weights, tables, one batch of
   // loads) and enough warps in flight to cover the memory latency even for a few thousand rows
@@ -56,7 +59,14 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
   const long long nunits = (long long)p.batch * p.rows * nhb;
   const long long wstride = (long long)gridDim.x * (blockDim.x >> 5);
   for (long long u = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nunits; u += wstride) {
-    const int rb = (int)(u / nhb), hb = (int)(u - (long long)rb * nhb) * 8;
+    int rb, hb;
+    if constexpr (KONLY) {
+      rb = (int)((unsigned)u / (unsigned)nhb);
+      hb = (int)((unsigned)u - (unsigned)rb * (unsigned)nhb) * 8;
+    } else {
+      rb = (int)(u / nhb);
+      hb = (int)(u - (long long)rb * nhb) * 8;
+    }
     const int b = rb / p.rows, row = rb - b * p.rows;
     const __nv_bfloat16* srow = p.src + (size_t)b * p.bs_src + (size_t)row * p.ld_src;
     __nv_bfloat16* drow = p.dst + (size_t)b * p.bs_dst + (size_t)row * p.ld_dst;
@@ -85,7 +95,7 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
         const int hh = hb + 2 * i + sub;
         live[i] = hh < heads;                      // ragged head count: idle lanes re-read the last head
         const int hc = live[i] ? hh : heads - 1;
-        isq[i] = hc < p.n_q;
+        isq[i] = !KONLY && hc < p.n_q;
         hl[i] = isq[i] ? hc : hc - p.n_q;
         const int scol = (isq[i] ? p.q_off : p.k_off) + hl[i] * 128 + 8 * c;
         dcol[i] = (isq[i] ? p.q_off_dst : p.k_off_dst) + hl[i] * 128 + 8 * c;
@@ -95,20 +105,27 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
       for (int i = 0; i < 4; i++) {
         if (hb + 2 * i >= heads) break;            // warp-uniform
         const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-        float y[8], z[8];
-        float ss = 0.f;
+        // packed fp32 pairs: the sum of squares and the scaling take half the instructions
+        uint64_t y2[4];
+        uint64_t acc2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
         for (int e = 0; e < 4; e++) {
-          y[2 * e] = bf16lo_to_f32(w4[e]);
-          y[2 * e + 1] = bf16hi_to_f32(w4[e]);
-          ss = fmaf(y[2 * e], y[2 * e], ss);
-          ss = fmaf(y[2 * e + 1], y[2 * e + 1], ss);
+          y2[e] = pack_f32x2(bf16lo_to_f32(w4[e]), bf16hi_to_f32(w4[e]));
+          acc2 = fma_f32x2(y2[e], y2[e], acc2);
         }
+        float s0, s1;
+        unpack_f32x2(acc2, s0, s1);
+        float ss = s0 + s1;
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         const float rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+        const uint64_t r2 = pack_f32x2(rrms, rrms);
+        float y[8], z[8];
 #pragma unroll
-        for (int e = 0; e < 8; e++) y[e] *= rrms * (isq[i] ? wqv[e] : wkv[e]);
+        for (int e = 0; e < 4; e++) {
+          const uint64_t w2 = isq[i] ? wq2[e] : wk2[e];
+          unpack_f32x2(mul_f32x2(y2[e], mul_f32x2(r2, w2)), y[2 * e], y[2 * e + 1]);
+        }
         if (MODE == 0) {
 #pragma unroll
           for (int e = 0; e < 4; e++) {
@@ -126,7 +143,7 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
 #pragma unroll
           for (int e = 0; e < 8; e++) z[e] = y[e];
         }
-        if (p.big_dim >= 0 && c == (p.big_dim >> 3)) {
+        if (!KONLY && p.big_dim >= 0 && c == (p.big_dim >> 3)) {
           // that channel goes to the fp32 side buffer and is stored as zero (norm.metal:127-132)
           const int e = p.big_dim & 7;
           float v = 0.f;
@@ -142,6 +159,11 @@ __global__ void __launch_bounds__(256, 3) qk_norm_rope_kernel(const NormRopePara
       }
     }
   }
+}
+
+template <int MODE, bool KONLY>
+static cudaError_t launch_norm_variant(const cudaLaunchConfig_t& cfg, const NormRopeParams& p) {
+  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<MODE, KONLY>, p);
 }
 
 cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
@@ -160,9 +182,15 @@ cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
-  if (p.rope_mode == 0) return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<0>, p);
-  if (p.rope_mode == 1) return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<1>, p);
-  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<2>, p);
+  const bool konly = p.n_q == 0 && p.big_dim < 0 && nunits < (1LL << 31);
+  if (konly) {
+    if (p.rope_mode == 0) return launch_norm_variant<0, true>(cfg, p);
+    if (p.rope_mode == 1) return launch_norm_variant<1, true>(cfg, p);
+    return launch_norm_variant<2, true>(cfg, p);
+  }
+  if (p.rope_mode == 0) return launch_norm_variant<0, false>(cfg, p);
+  if (p.rope_mode == 1) return launch_norm_variant<1, false>(cfg, p);
+  return launch_norm_variant<2, false>(cfg, p);
 }
 
 // ---- sequence <-> head resharding (pack / unpack around an all-to-all) -------------------------------

@@ -384,11 +384,12 @@ def test_sequence_parallel_entry_points_on_one_rank(kc):
 
 
 @pytest.mark.parametrize("env", [{"KREA_CUDA_SPLIT": "2"}, {"KREA_CUDA_EMU": "1"}, {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_EMU": "1"},
-                                 {"KREA_CUDA_STATIC_BOUND": "0"}])
+                                 {"KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PDL": "0"}, {"KREA_CUDA_O_TMA": "0"},
+                                 {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_O_TMA": "0", "KREA_CUDA_PDL": "0"}])
 def test_tuning_knob_variants(monkeypatch, env):
     """The build-time variants a handle can select through its environment (two softmax threads per row,
-    polynomial exp2 for a quarter of the elements, online max instead of the a-priori bound) give the
-    same results within tolerance, including a ragged key tail, GQA and the padding mask."""
+    polynomial exp2 for a quarter of the elements, online max instead of the a-priori bound, plain instead
+    of programmatic launch, copy loop instead of TMA output stores) give the same results within tolerance, including a ragged key tail, GQA and the padding mask."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     k2 = ops.KreaCuda(0)

@@ -211,6 +211,37 @@ typedef struct {
 } krea_cuda_layerwise_args;
 KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwise_args* a);
 
+/* ---- Metal::gemm, bf16 weights, EPI_BF16 (engine/src/metal.h:64-67; kernels/gemm.metal:29-30, 251-279) ----
+ * C[M, N] (bf16, row stride ldc) = A[M, K] (bf16, row stride lda) x Wt[K, N] (bf16, row stride ldw): the
+ * reference's operand layouts, weights "input-major" as tools/convert.py lays them out.  This is the
+ * projection either side of the attention (the fused q|k|v|gate product, engine/src/model.mm:349-359).
+ * KREA_CUDA_EPI_QKNORM_ROPE additionally applies Metal::qk_norm_rope (norm.metal:81-134) to the n_q head
+ * blocks of 128 output columns starting at q_off and the n_k blocks starting at k_off before the store, so
+ * the projection writes Q and K already normalised and rotated (rope_mode 0 or 2; cos/sin row = row0 + output
+ * row); the attention is then called through krea_cuda_attention on the result.
+ * Not built: int8 weights with group scales (Weight::q8), the other epilogues, the LoRA term -> E_UNSUPPORTED
+ * is not needed because they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
+#define KREA_CUDA_EPI_BF16 0
+#define KREA_CUDA_EPI_QKNORM_ROPE 1
+typedef struct {
+  const void* A;
+  const void* W;
+  void* C;
+  int M, N, K;
+  int lda, ldw, ldc;
+  int epilogue;
+  int q_off, n_q, k_off, n_k;
+  const float* wq;
+  const float* wk;
+  const float* cos;
+  const float* sin;
+  int row0;
+  float eps;
+  int rope_mode;
+} krea_cuda_gemm_args;
+KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
+
 /* ---- `.qw` weight files (the reference's WeightFile, engine/src/weights.h:26-75, weights.mm:16-81; format
  * written by tools/convert.py:49-89) ----
  * The on-disk format that supplies the path's QK-norm weights `L<l>.qn` / `L<l>.kn` (f32[128]):

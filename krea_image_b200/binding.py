@@ -11,6 +11,7 @@ from . import build as _build
 
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM, E_COMM, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
+EPI_BF16, EPI_QKNORM_ROPE = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20   # KREA_CUDA_STATIC_SCRATCH_BYTES
 DIST_ID_BYTES = 128                # KREA_CUDA_DIST_ID_BYTES
 
@@ -55,6 +56,13 @@ class LayerwiseArgs(ctypes.Structure):
                 ("q_off", _int), ("k_off", _int), ("v_off", _int), ("g_off", _int)]
 
 
+class GemmArgs(ctypes.Structure):
+    _fields_ = [("A", _vp), ("W", _vp), ("C", _vp), ("M", _int), ("N", _int), ("K", _int),
+                ("lda", _int), ("ldw", _int), ("ldc", _int), ("epilogue", _int),
+                ("q_off", _int), ("n_q", _int), ("k_off", _int), ("n_k", _int),
+                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int)]
+
+
 class QwInfo(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("dtype", ctypes.c_char_p), ("rank", _int), ("shape", _i64 * 8),
                 ("offset", ctypes.c_uint64), ("nbytes", ctypes.c_uint64)]
@@ -90,6 +98,7 @@ SYMBOLS = {
     "krea_cuda_joint_attention_static": (_int, [_vp, ctypes.POINTER(JointArgs)]),
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
+    "krea_cuda_gemm": (_int, [_vp, ctypes.POINTER(GemmArgs)]),
     "krea_cuda_layerwise_attn": (_int, [_vp, ctypes.POINTER(LayerwiseArgs)]),
     "krea_cuda_qw_open": (_vp, [ctypes.c_char_p, ctypes.c_char_p, _int]),
     "krea_cuda_qw_close": (None, [_vp]),

@@ -108,4 +108,23 @@ struct LayerwiseParams {
 };
 cudaError_t launch_layerwise_attn(const LayerwiseParams& p, cudaStream_t stream);
 
+// bf16 GEMM C = A x Wt with optional fused QK-norm + RoPE epilogue (gemm_sm100.cu).  Strides in elements.
+struct GemmParams {
+  __nv_bfloat16* C;
+  int64_t ldc;
+  int M, N, K;
+  int epi;                      // 0: bf16 store; 1: Q / K head blocks are RMS-normalised, weighted and rotated first
+  int q_off, n_q, k_off, n_k;   // epi 1: output columns of the Q and K heads (multiples of 128) and head counts
+  const float* wq;
+  const float* wk;
+  const float* cos;
+  const float* sin;
+  int row0;                     // table row of output row 0
+  float eps;
+  int rope_mode;                // 0 interleaved pairs, 2 none
+  uint32_t* status;
+};
+// A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream);
+
 }  // namespace krea

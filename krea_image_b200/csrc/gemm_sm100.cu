@@ -1,0 +1,255 @@
+// bf16 GEMM for B200 (sm_100a) with the epilogues the attention path's neighbours need:
+//   C[M, N] = A[M, K] (bf16, row stride lda) x Wt[K, N] (bf16, row stride ldw, "input-major" weights)
+// the operand layouts of the reference's Metal::gemm (engine/src/metal.h:64-67, kernels/gemm.metal:1-6).
+// EPI_BF16 stores the product as bf16 (gemm.metal:29-30); EPI_QKNORM additionally applies, to the head
+// blocks of 128 output columns that hold Q and K, the per-head RMSNorm x weight + RoPE of
+// engine/kernels/norm.metal:81-134 before the store - the projection that feeds the attention
+// (engine/src/model.mm:349-359, 376) then writes Q and K already normalised and rotated, and the separate
+// pass over them disappears.
+//
+// Shares nothing with the reference's simdgroup kernels:
+//   * persistent CTAs walk 128 x 256 output tiles; one warp issues TMA loads of A (K-major) and Wt (N-major,
+//     exactly as it lies in memory) into a 4-stage ring of 128B-swizzled shared memory, one warp issues
+//     tcgen05.mma (M128 N256 K16) into one of two 256-column accumulators in tensor memory, four warps
+//     drain the other accumulator - the epilogue of tile i overlaps the main loop of tile i + 1;
+//   * a thread of the epilogue owns one output row (= one TMEM lane), so a head's 128 columns - its sum of
+//     squares, its rotation pairs - are all in that thread's registers: the fused norm needs no exchange;
+//   * every wait is bounded (status word, normal exit) as in the attention kernel.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "attention_sm100.h"
+#include "sm100_ptx.cuh"
+
+namespace krea {
+
+namespace gemm {
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB: [128 rows][64 k], K-major
+constexpr int B_BYTES = BK * BN * 2;          // 32 KB: four blocks of [64 k][64 n], N-major
+constexpr int B_BLOCK = BK * 64 * 2;          // 8 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 256;                  // warp 0 TMA, warp 1 MMA, warps 4-7 epilogue
+constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
+enum : uint32_t { SITE_FULL = 11, SITE_EMPTY = 12, SITE_ACC_FULL = 13, SITE_ACC_EMPTY = 14 };
+}  // namespace gemm
+
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
+  using namespace gemm;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                 // [STAGES] TMA landed
+  uint64_t* empty = bars + STAGES;       // [STAGES] MMAs that read the stage have finished
+  uint64_t* acc_full = empty + STAGES;   // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + 2;    // [2] accumulator drained by the epilogue warps
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile uint32_t* abort_word = (volatile uint32_t*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = (p.M + BM - 1) / BM, nt = (p.N + BN - 1) / BN;
+  const int tiles = mt * nt, kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    abort_word[0] = (p.status != nullptr && *p.status != 0u) ? 0xFFu : 0u;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile t -> (m tile, n tile): m fastest, so the CTAs running together share a few column blocks of Wt
+  // (read from HBM once) while A stays in L2
+  if (warp == 0) {
+    // ======================================= TMA producer =======================================
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmW);
+      uint32_t n = 0;     // k-blocks issued so far
+      for (int t = blockIdx.x; t < tiles && *abort_word == 0u; t += gridDim.x) {
+        const int m0 = (t % mt) * BM, n0 = (t / mt) * BN;
+        for (int kb = 0; kb < kblocks; kb++, n++) {
+          const int s = n % STAGES;
+          if (!mbar_wait(&empty[s], ((n / STAGES) & 1) ^ 1, abort_word, SITE_EMPTY)) break;
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_BYTES;
+          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_3d(a_dst, &tmA, &full[s], kb * BK, m0, 0);
+#pragma unroll
+          for (int j = 0; j < BN / 64; j++) tma_load_3d(b_dst + j * B_BLOCK, &tmW, &full[s], n0 + j * 64, kb * BK, 0);
+        }
+      }
+      // nothing may still be in flight into this CTA's shared memory when it exits
+      if (*abort_word != 0u) {
+        for (uint32_t i = (n > STAGES ? n - STAGES : 0); i < n; i++)
+          mbar_wait_slow(&full[i % STAGES], (i / STAGES) & 1, abort_word + 1, SITE_FULL);
+      }
+    }
+  } else if (warp == 1) {
+    // ======================================== MMA issuer ========================================
+    const bool leader = elect_one();
+    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, true);
+    constexpr uint32_t HI = desc_hi(1024);
+    constexpr uint32_t LBO_A = (16u >> 4) << 16;                       // K-major: unused
+    constexpr uint32_t LBO_B = ((uint32_t)B_BLOCK >> 4) << 16;         // N-major: next 64 columns 8 KB away
+    const uint32_t smem_lo = smem_u32(smem) >> 4;
+    uint32_t n = 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+      const int a = it & 1;
+      if (it >= 2) {
+        if (!mbar_wait(&acc_empty[a], ((it >> 1) - 1) & 1, abort_word, SITE_ACC_EMPTY)) break;
+        tc_fence_after();
+      }
+      const uint32_t d_tmem = tmem_base + a * BN;
+      for (int kb = 0; kb < kblocks; kb++, n++) {
+        const int s = n % STAGES;
+        if (!mbar_wait(&full[s], (n / STAGES) & 1, abort_word, SITE_FULL)) break;
+        tc_fence_after();
+        const uint32_t a_lo = (smem_lo + s * (STAGE_BYTES >> 4)) | LBO_A;
+        const uint32_t b_lo = (smem_lo + s * (STAGE_BYTES >> 4) + (A_BYTES >> 4)) | LBO_B;
+#pragma unroll
+        for (int k = 0; k < BK / 16; k++) {
+          const uint64_t da = make_desc(a_lo + k * 2, HI), db = make_desc(b_lo + k * 128, HI);   // 32 B / 2048 B per 16 k
+          if (leader) {
+            if (kb == 0 && k == 0) umma_ss<false>(d_tmem, da, db, idesc);
+            else umma_ss<true>(d_tmem, da, db, idesc);
+          }
+        }
+        if (leader) umma_commit(&empty[s]);
+        __syncwarp();
+      }
+      if (leader) umma_commit(&acc_full[a]);
+      __syncwarp();
+      if (*abort_word != 0u) break;
+    }
+  } else if (warp >= 4) {
+    // ========================================= epilogue =========================================
+    const int r = (warp & 3) * 32 + lane;                 // row of the tile = TMEM lane
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    int it = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+      const int a = it & 1;
+      const int m0 = (t % mt) * BM, n0 = (t / mt) * BN;
+      if (!mbar_wait(&acc_full[a], (it >> 1) & 1, abort_word, SITE_ACC_FULL)) break;
+      tc_fence_after();
+      const int row = m0 + r;
+      __nv_bfloat16* crow = p.C + (size_t)min(row, p.M - 1) * p.ldc;
+#pragma unroll 1
+      for (int hb = 0; hb < BN / 128; hb++) {             // one block of 128 columns (one head) at a time
+        const int col0 = n0 + hb * 128;
+        if (col0 >= p.N) break;
+        // which treatment this block of columns gets: 0 plain, 1 Q head, 2 K head
+        int kind = 0;
+        if (p.epi == 1) {
+          if (col0 >= p.q_off && col0 < p.q_off + p.n_q * 128) kind = 1;
+          else if (col0 >= p.k_off && col0 < p.k_off + p.n_k * 128) kind = 2;
+        }
+        float rrms = 1.f;
+        if (kind != 0) {
+          // pass 1 over the accumulator: sum of squares of the row's 128 values of this head
+          float ss = 0.f;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + a * BN + hb * 128 + c0, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; e++) ss = fmaf(__uint_as_float(v[e]), __uint_as_float(v[e]), ss);
+          }
+          rrms = rsqrtf(ss * (1.0f / 128.0f) + p.eps);                       // norm.metal:102
+        }
+        const float* w = kind == 1 ? p.wq : p.wk;
+        const size_t trow = (size_t)(p.row0 + min(row, p.M - 1)) * 64;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(lane_addr + a * BN + hb * 128 + c0, v);
+          tmem_wait_ld();
+          float f[32];
+#pragma unroll
+          for (int e = 0; e < 32; e++) f[e] = __uint_as_float(v[e]);
+          if (kind != 0) {
+#pragma unroll
+            for (int e4 = 0; e4 < 8; e4++) {
+              const float4 wv = __ldg((const float4*)(w + c0) + e4);
+              f[4 * e4] *= rrms * wv.x; f[4 * e4 + 1] *= rrms * wv.y; f[4 * e4 + 2] *= rrms * wv.z; f[4 * e4 + 3] *= rrms * wv.w;
+            }
+            if (p.rope_mode == 0) {
+              // interleaved pairs (2i, 2i+1) turn by the row's entry i (norm.metal:105-113): pairs c0/2 .. c0/2+15
+#pragma unroll
+              for (int e4 = 0; e4 < 4; e4++) {
+                const float4 cc = __ldg((const float4*)(p.cos + trow + (c0 >> 1)) + e4), sc = __ldg((const float4*)(p.sin + trow + (c0 >> 1)) + e4);
+                const float cf[4] = {cc.x, cc.y, cc.z, cc.w}, sf[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                  const float x0 = f[8 * e4 + 2 * q], x1 = f[8 * e4 + 2 * q + 1];
+                  f[8 * e4 + 2 * q] = x0 * cf[q] - x1 * sf[q];
+                  f[8 * e4 + 2 * q + 1] = x0 * sf[q] + x1 * cf[q];
+                }
+              }
+            }
+          }
+          if (row < p.M) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int col = col0 + c0 + q4 * 8;
+              if (col + 8 <= p.N)
+                *(uint4*)(crow + col) = make_uint4(pack_bf16x2(f[q4 * 8], f[q4 * 8 + 1]), pack_bf16x2(f[q4 * 8 + 2], f[q4 * 8 + 3]),
+                                                   pack_bf16x2(f[q4 * 8 + 4], f[q4 * 8 + 5]), pack_bf16x2(f[q4 * 8 + 6], f[q4 * 8 + 7]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[a]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && p.status != nullptr) {
+    const uint32_t a = *abort_word;
+    if (a != 0u && a != 0xFFu) atomicCAS(p.status, 0u, a | ((uint32_t)blockIdx.x << 8));
+  }
+}
+
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream) {
+  using namespace gemm;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  if (tiles <= 0 || p.K <= 0) return cudaSuccess;
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_bf16_sm100<<<grid, THREADS, SMEM, stream>>>(tmA, tmW, p);
+  return cudaGetLastError();
+}
+
+}  // namespace krea

@@ -44,6 +44,7 @@ struct krea_cuda {
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[4];   // pending (start, stop) pairs per kind of work
   std::vector<cudaEvent_t> event_pool;
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
+  int sm_count = 0;                 // SMs of the device (persistent kernels size their grid by it)
   void* qw_stage = nullptr;         // pinned staging of krea_cuda_qw_upload (two 8 MiB halves)
 };
 

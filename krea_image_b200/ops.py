@@ -136,6 +136,21 @@ class KreaCuda:
         a.Lk, a.heads, a.group, a.batch = Lk, heads, group, batch
         return int(self.lib.krea_cuda_joint_scratch_bytes(ctypes.byref(a)))
 
+    def gemm(self, A, W, C, M, N, K, lda, ldw, ldc, *, qk_norm=None):
+        """Metal::gemm with Epi::BF16 (engine/src/metal.h:64-67): C[M,N] = A[M,K] x Wt[K,N], bf16.
+        qk_norm = dict(q_off, n_q, k_off, n_k, wq, wk, cos, sin, row0, eps, rope_mode) fuses Metal::qk_norm_rope
+        on those head blocks into the store."""
+        a = B.GemmArgs()
+        a.A, a.W, a.C = _ptr(A), _ptr(W), _ptr(C)
+        a.M, a.N, a.K, a.lda, a.ldw, a.ldc = M, N, K, lda, ldw, ldc
+        if qk_norm is not None:
+            a.epilogue = B.EPI_QKNORM_ROPE
+            a.q_off, a.n_q, a.k_off, a.n_k = qk_norm["q_off"], qk_norm["n_q"], qk_norm["k_off"], qk_norm["n_k"]
+            a.wq, a.wk = _ptr(qk_norm.get("wq")), _ptr(qk_norm.get("wk"))
+            a.cos, a.sin = _ptr(qk_norm.get("cos")), _ptr(qk_norm.get("sin"))
+            a.row0, a.eps, a.rope_mode = qk_norm.get("row0", 0), qk_norm.get("eps", 1e-6), qk_norm.get("rope_mode", B.ROPE_PAIRS)
+        self._check(self.lib.krea_cuda_gemm(self.h, ctypes.byref(a)))
+
     def layerwise_attn(self, qkvg, out, rows, ld, ldo, heads, q_off, k_off, v_off, g_off):
         """Metal::layerwise_attn (engine/src/metal.h:90-91): same argument order."""
         a = B.LayerwiseArgs(_ptr(qkvg), _ptr(out), rows, ld, ldo, heads, q_off, k_off, v_off, g_off)

@@ -1,0 +1,116 @@
+"""GPU parity of the projection GEMM next to the attention (Metal::gemm with Epi::BF16, engine/src/metal.h:64-67)
+and of its fused QK-norm + RoPE epilogue (gemm followed by Metal::qk_norm_rope in the reference,
+engine/src/model.mm:349-359, 376) against float64 / float32 numpy statements of the same math."""
+import numpy as np
+import pytest
+import torch
+
+from krea_image_b200 import binding, ops, synth
+from oracle import oracle_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def kc():
+    k = ops.KreaCuda(0)
+    k.set_stream(torch.cuda.current_stream())
+    yield k
+    k.close()
+
+
+def _bits(a):
+    return synth.f32_to_bf16_bits(np.ascontiguousarray(a, dtype=np.float32)).reshape(a.shape)
+
+
+def _dev(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).cuda().view(torch.bfloat16)
+
+
+def _case(seed, M, N, K, lda, ldw):
+    rng = np.random.default_rng(seed)
+    a = _bits(rng.standard_normal((M, lda)))
+    w = _bits(rng.standard_normal((K, ldw)) / np.sqrt(K))
+    return a, w
+
+
+def _rel(got, want):
+    d = got.astype(np.float64) - want
+    return np.linalg.norm(d) / max(np.linalg.norm(want), 1e-30), np.abs(d).max()
+
+
+@pytest.mark.parametrize("M,N,K,pad", [(128, 256, 64, 0), (1, 8, 8, 0), (300, 520, 200, 8), (257, 1000, 72, 16), (1024, 768, 2048, 0)])
+def test_gemm_bf16_shapes(kc, M, N, K, pad):
+    lda, ldw, ldc = K + pad, N + pad, N + 2 * pad
+    a, w = _case(M + N + K, M, N, K, lda, ldw)
+    want = synth.bf16_bits_to_f32(a[:, :K]).astype(np.float64) @ synth.bf16_bits_to_f32(w[:, :N]).astype(np.float64)
+    c = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+    n0 = kc.launches
+    kc.gemm(_dev(a), _dev(w), c, M, N, K, lda, ldw, ldc)
+    kc.wait()
+    assert kc.launches - n0 == 1
+    got = c.float().cpu().numpy()
+    rel, mx = _rel(got[:, :N], want)
+    assert rel <= 3e-3, f"rel-L2 {rel:.3e} max-abs {mx:.3e}"          # one bf16 rounding of the output: ~1.7e-3
+    assert np.all(np.isnan(got[:, N:]))                                # nothing written past column N
+
+
+def test_gemm_fused_qk_norm_rope(kc):
+    """q|k|v projection of a small model (4 heads, S = 400 with a 16 x 20 grid): Q and K blocks come out
+    normalised and rotated, V plain; the result drives the attention operator and matches the oracle chain."""
+    import oracle
+    H, T, gh, gw, K = 4, 80, 16, 20, 320
+    S = T + gh * gw
+    N = 3 * H * 128
+    a, w = _case(5, S, N, K, K, N)
+    rng = np.random.default_rng(6)
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    cos, sin = synth.rope_tables_axial2d(T, gh, gw)
+    y = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)       # [S, N]
+    want = y.copy()
+    for h in range(H):
+        want[:, h * 128:(h + 1) * 128] = oracle_np.norm_rope(y[:, h * 128:(h + 1) * 128], wq.astype(np.float64), cos, sin, 1e-6, 0)
+        want[:, (H + h) * 128:(H + h + 1) * 128] = oracle_np.norm_rope(y[:, (H + h) * 128:(H + h + 1) * 128], wk.astype(np.float64), cos, sin, 1e-6, 0)
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    d_wq, d_wk, d_cos, d_sin = dev(wq), dev(wk), dev(cos), dev(sin)
+    c = torch.zeros((S, N), dtype=torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), _dev(w), c, S, N, K, K, N, N,
+            qk_norm=dict(q_off=0, n_q=H, k_off=H * 128, n_k=H, wq=d_wq, wk=d_wk, cos=d_cos, sin=d_sin, row0=0, eps=1e-6, rope_mode=0))
+    kc.wait()
+    got = c.float().cpu().numpy()
+    for name, lo, hi in (("Q", 0, H * 128), ("K", H * 128, 2 * H * 128), ("V", 2 * H * 128, N)):
+        rel, mx = _rel(got[:, lo:hi], want[:, lo:hi])
+        assert rel <= 3e-3, f"{name}: rel-L2 {rel:.3e} max-abs {mx:.3e}"
+    # ... and the attention operator on the projected, already normalised rows against the oracle's attention on the same bits
+    cb = c.view(torch.int16).cpu().numpy().view(np.uint16)
+    o = torch.zeros((S, H * 128), dtype=torch.bfloat16, device="cuda")
+    cf = c.view(-1)
+    kc.attention(cf, cf[H * 128:], cf[2 * H * 128:], o, S, S, H, N, N, N, H * 128, 1)
+    kc.wait()
+    flat = cb.reshape(-1)
+    want_o = oracle.attention(flat, flat[H * 128:], flat[2 * H * 128:], S, S, H, N, N, N)
+    rel, mx = _rel(o.float().cpu().numpy(), want_o)
+    assert rel <= 5e-3 and mx <= 2e-2
+    # errors: rotate-half is not fused, head blocks must sit on 128-column boundaries
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.gemm(_dev(a), _dev(w), c, S, N, K, K, N, N, qk_norm=dict(q_off=0, n_q=H, k_off=H * 128, n_k=H, wq=d_wq, wk=d_wk, cos=d_cos, sin=d_sin, rope_mode=1))
+    assert e.value.code == binding.E_UNSUPPORTED
+    with pytest.raises(ops.KreaCudaError):
+        kc.gemm(_dev(a), _dev(w), c, S, N, K, K, N, N, qk_norm=dict(q_off=64, n_q=H, k_off=H * 128, n_k=H, wq=d_wq, wk=d_wk, cos=d_cos, sin=d_sin))
+    with pytest.raises(ops.KreaCudaError):
+        kc.gemm(_dev(a), _dev(w), c, S, N + 4, K, K, N, N)
+
+
+def test_gemm_model_size_projection(kc):
+    """The q|k|v projection at the headline configuration's size (4608 x 9216 x 3072) against float32 numpy."""
+    M, N, K = 4608, 9216, 3072
+    a, w = _case(11, M, N, K, K, N)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N)
+    kc.wait()
+    rows = np.arange(0, M, 37)
+    want = synth.bf16_bits_to_f32(a[rows]) @ synth.bf16_bits_to_f32(w)
+    got = c[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    rel, mx = _rel(got, want)
+    assert rel <= 3e-3, f"rel-L2 {rel:.3e} max-abs {mx:.3e}"

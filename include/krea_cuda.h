@@ -219,11 +219,14 @@ KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwi
  * blocks of 128 output columns starting at q_off and the n_k blocks starting at k_off before the store, so
  * the projection writes Q and K already normalised and rotated (rope_mode 0 or 2; cos/sin row = row0 + output
  * row); the attention is then called through krea_cuda_attention on the result.
- * Not built: int8 weights with group scales (Weight::q8), the other epilogues, the LoRA term -> E_UNSUPPORTED
- * is not needed because they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * KREA_CUDA_EPI_RESID_GATE / _SWIGLU are the epilogues of the O-projection and of the MLP (model.mm:357-366).
+ * Not built: int8 weights with group scales (Weight::q8), the F32 / GELU / bias epilogues, the LoRA term, the
+ * column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
  * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
 #define KREA_CUDA_EPI_BF16 0
 #define KREA_CUDA_EPI_QKNORM_ROPE 1
+#define KREA_CUDA_EPI_RESID_GATE 2 /* C is f32 [M, N]: C += vec[n] * acc (gemm.metal:262-264); vec NULL: C += acc (Epi::Resid) */
+#define KREA_CUDA_EPI_SWIGLU 3     /* C is bf16 [M, N/2]: silu(gate) * up on tile-interleaved weights (gemm.metal:233-250); N % 64 == 0 */
 typedef struct {
   const void* A;
   const void* W;
@@ -239,6 +242,7 @@ typedef struct {
   int row0;
   float eps;
   int rope_mode;
+  const float* vec;   /* RESID_GATE: per-column gate, f32 [N] (the reference's `vec` argument) */
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
 

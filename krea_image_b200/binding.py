@@ -11,7 +11,7 @@ from . import build as _build
 
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM, E_COMM, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
-EPI_BF16, EPI_QKNORM_ROPE = 0, 1
+EPI_BF16, EPI_QKNORM_ROPE, EPI_RESID_GATE, EPI_SWIGLU = 0, 1, 2, 3
 STATIC_SCRATCH_BYTES = 32 << 20   # KREA_CUDA_STATIC_SCRATCH_BYTES
 DIST_ID_BYTES = 128                # KREA_CUDA_DIST_ID_BYTES
 
@@ -60,7 +60,7 @@ class GemmArgs(ctypes.Structure):
     _fields_ = [("A", _vp), ("W", _vp), ("C", _vp), ("M", _int), ("N", _int), ("K", _int),
                 ("lda", _int), ("ldw", _int), ("ldc", _int), ("epilogue", _int),
                 ("q_off", _int), ("n_q", _int), ("k_off", _int), ("n_k", _int),
-                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int)]
+                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int), ("vec", _vp)]
 
 
 class QwInfo(ctypes.Structure):

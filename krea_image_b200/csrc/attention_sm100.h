@@ -113,7 +113,9 @@ struct GemmParams {
   __nv_bfloat16* C;
   int64_t ldc;
   int M, N, K;
-  int epi;                      // 0: bf16 store; 1: Q / K head blocks are RMS-normalised, weighted and rotated first
+  int epi;                      // 0: bf16 store; 1: Q / K head blocks are RMS-normalised, weighted and rotated first;
+                                // 2: C is fp32 and receives += vec[col] * acc (vec nullptr: += acc); 3: SwiGLU, C has N / 2 columns
+  const float* vec;             // epi 2: per-column gate
   int q_off, n_q, k_off, n_k;   // epi 1: output columns of the Q and K heads (multiples of 128) and head counts
   const float* wq;
   const float* wk;

@@ -152,6 +152,58 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_after();
       const int row = m0 + r;
       __nv_bfloat16* crow = p.C + (size_t)min(row, p.M - 1) * p.ldc;
+      if (p.epi == 2) {
+        // X(f32)[row, col] += vec[col] * acc (gated residual, gemm.metal:262-264); vec == nullptr: X += acc (:265-267)
+        float* xrow = (float*)p.C + (size_t)min(row, p.M - 1) * p.ldc;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          const int col0 = n0 + c0;
+          if (col0 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld32(lane_addr + a * BN + c0, v);
+          tmem_wait_ld();
+          if (row < p.M) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; q4++) {
+              const int col = col0 + q4 * 4;
+              if (col + 4 <= p.N) {
+                float4 x = *(float4*)(xrow + col);
+                const float4 gt = p.vec ? __ldg((const float4*)(p.vec + col)) : make_float4(1.f, 1.f, 1.f, 1.f);
+                x.x = fmaf(gt.x, __uint_as_float(v[q4 * 4]), x.x);
+                x.y = fmaf(gt.y, __uint_as_float(v[q4 * 4 + 1]), x.y);
+                x.z = fmaf(gt.z, __uint_as_float(v[q4 * 4 + 2]), x.z);
+                x.w = fmaf(gt.w, __uint_as_float(v[q4 * 4 + 3]), x.w);
+                *(float4*)(xrow + col) = x;
+              }
+            }
+          }
+        }
+      } else if (p.epi == 3) {
+        // SwiGLU on tile-interleaved weights (gemm.metal:233-250): every 64 weight columns hold 32 gate columns,
+        // then the 32 matching up columns; output column (n / 64) * 32 + i = silu(gate_i) * up_i, bf16
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          const int col0 = n0 + c0;
+          if (col0 >= p.N) break;
+          uint32_t g[32], u[32];
+          tmem_ld32(lane_addr + a * BN + c0, g);
+          tmem_ld32(lane_addr + a * BN + c0 + 32, u);
+          tmem_wait_ld();
+          if (row < p.M) {
+            const int ocol0 = (col0 >> 6) * 32;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; e++) {
+                const float gv = __uint_as_float(g[q4 * 8 + e]);
+                f[e] = gv / (1.0f + __expf(-gv)) * __uint_as_float(u[q4 * 8 + e]);      // common.h silu
+              }
+              *(uint4*)(crow + ocol0 + q4 * 8) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int hb = 0; hb < BN / 128; hb++) {             // one block of 128 columns (one head) at a time
         const int col0 = n0 + hb * 128;

@@ -102,6 +102,43 @@ def test_gemm_fused_qk_norm_rope(kc):
         kc.gemm(_dev(a), _dev(w), c, S, N + 4, K, K, N, N)
 
 
+@pytest.mark.parametrize("with_gate", [True, False])
+def test_gemm_gated_residual_epilogue(kc, with_gate):
+    """Epi::ResidGate / Epi::Resid (gemm.metal:262-267): the fp32 residual stream receives += gate[n] * acc."""
+    M, N, K = 333, 520, 264
+    a, w = _case(21, M, N, K, K, N)
+    rng = np.random.default_rng(22)
+    x0 = rng.standard_normal((M, N + 8)).astype(np.float32)
+    gate = np.tanh(rng.standard_normal(N)).astype(np.float32)
+    acc = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+    want = x0[:, :N] + (gate[None, :] if with_gate else 1.0) * acc
+    x = torch.from_numpy(x0).cuda()
+    kc.gemm(_dev(a), _dev(w), x, M, N, K, K, N, N + 8, epilogue=binding.EPI_RESID_GATE, vec=torch.from_numpy(gate).cuda() if with_gate else None)
+    kc.wait()
+    got = x.cpu().numpy()
+    assert np.allclose(got[:, :N], want, rtol=1e-4, atol=1e-4)       # fp32 in, fp32 out: only accumulation order differs
+    assert np.array_equal(got[:, N:], x0[:, N:])                       # columns past N untouched
+
+
+def test_gemm_swiglu_epilogue(kc):
+    """Epi::SwiGLU (gemm.metal:233-250): weight columns come in groups of 64 = 32 gate + 32 up columns."""
+    M, H1, K = 200, 160, 136          # N = 2 * H1 = 320 = five groups of 64
+    N = 2 * H1
+    a, w = _case(31, M, N, K, K, N)
+    acc = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+    g = acc.reshape(M, N // 64, 2, 32)
+    want = (g[:, :, 0] / (1.0 + np.exp(-g[:, :, 0])) * g[:, :, 1]).reshape(M, H1)
+    c = torch.full((M, H1 + 8), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, H1 + 8, epilogue=binding.EPI_SWIGLU)
+    kc.wait()
+    got = c.float().cpu().numpy()
+    rel, mx = _rel(got[:, :H1], want)
+    assert rel <= 3e-3, f"rel-L2 {rel:.3e} max-abs {mx:.3e}"
+    assert np.all(np.isnan(got[:, H1:]))
+    with pytest.raises(ops.KreaCudaError):
+        kc.gemm(_dev(a), _dev(w), c, M, N - 32, K, K, N, H1 + 8, epilogue=binding.EPI_SWIGLU)   # not a whole number of groups
+
+
 def test_gemm_model_size_projection(kc):
     """The q|k|v projection at the headline configuration's size (4608 x 9216 x 3072) against float32 numpy."""
     M, N, K = 4608, 9216, 3072

@@ -246,6 +246,52 @@ typedef struct {
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
 
+/* ---- Metal::rms_norm (engine/src/metal.h:75-77; kernel norm.metal:28-55) ----
+ * y[row, c] = x[row, c] * rsqrt(mean_c(x[row]^2) + eps) * mul[c] (+ add[c]); x f32 [rows, ld_in], y bf16 (or f32
+ * when f32_out) [rows, ld_out]; width, ld_in, ld_out multiples of 4 (8 for bf16 output); add may be NULL. */
+typedef struct {
+  const float* x;
+  const float* mul;
+  const float* add;
+  void* y;
+  int rows, width, ld_in, ld_out;
+  float eps;
+  int f32_out;
+} krea_cuda_rmsnorm_args;
+KREA_CUDA_API int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args* a);
+
+/* ---- one DiT block, DiT::layer (engine/src/model.mm:369-385) ----
+ * x (the fp32 residual stream [rows, dim], dim = heads * 128) is updated in place:
+ *   h = rms_norm(x, mul1, add1);  q|k|v|gate = h Wqkvg with per-head QK-norm + RoPE on q and k;
+ *   ao = attention(q, k, v) * sigmoid(gate);  x += gate1 * (ao Wo);
+ *   h = rms_norm(x, mul2, add2);  mid = swiglu(h Wgu);  x += gate2 * (mid Wdown).
+ * mods: the six modulation vectors of `dim` floats in that order (mul1, add1, gate1, mul2, add2, gate2), as
+ * the reference lays them out per layer (model.mm:371-372).  Weights are bf16, input-major ([K, N]), Wgu with
+ * gate / up columns interleaved in groups of 32 (tools/convert.py); column layout of the fused projection:
+ * q [heads*128] | k [kv_heads*128] | v [kv_heads*128] | gate [heads*128] (model.mm:282-288).  The rows are
+ * [text ; image] tokens; cos / sin are their [rows, 64] tables.  Seven kernels: two norms, four GEMMs (the
+ * first with the fused QK-norm epilogue) and the attention.  Not handled here: int8 weights, the fp32
+ * big-dimension split of the reference's block 0, the GPU/ANE hybrid schedule.
+ * Workspace: krea_cuda_dit_block_workspace_bytes; pass a buffer or let the handle own one. */
+typedef struct {
+  float* x;
+  const float* mods;
+  const void* w_qkvg;
+  const void* w_o;
+  const void* w_gu;
+  const void* w_down;
+  const float* qn;
+  const float* kn;
+  const float* cos;
+  const float* sin;
+  int rows, heads, kv_heads, ff;
+  float eps;
+  void* workspace;
+  size_t workspace_bytes;
+} krea_cuda_dit_block_args;
+KREA_CUDA_API size_t krea_cuda_dit_block_workspace_bytes(const krea_cuda_dit_block_args* a);
+KREA_CUDA_API int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a);
+
 /* ---- `.qw` weight files (the reference's WeightFile, engine/src/weights.h:26-75, weights.mm:16-81; format
  * written by tools/convert.py:49-89) ----
  * The on-disk format that supplies the path's QK-norm weights `L<l>.qn` / `L<l>.kn` (f32[128]):

@@ -63,6 +63,18 @@ class GemmArgs(ctypes.Structure):
                 ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int), ("vec", _vp)]
 
 
+class RmsNormArgs(ctypes.Structure):
+    _fields_ = [("x", _vp), ("mul", _vp), ("add", _vp), ("y", _vp), ("rows", _int), ("width", _int), ("ld_in", _int),
+                ("ld_out", _int), ("eps", ctypes.c_float), ("f32_out", _int)]
+
+
+class DitBlockArgs(ctypes.Structure):
+    _fields_ = [("x", _vp), ("mods", _vp), ("w_qkvg", _vp), ("w_o", _vp), ("w_gu", _vp), ("w_down", _vp),
+                ("qn", _vp), ("kn", _vp), ("cos", _vp), ("sin", _vp),
+                ("rows", _int), ("heads", _int), ("kv_heads", _int), ("ff", _int), ("eps", ctypes.c_float),
+                ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t)]
+
+
 class QwInfo(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("dtype", ctypes.c_char_p), ("rank", _int), ("shape", _i64 * 8),
                 ("offset", ctypes.c_uint64), ("nbytes", ctypes.c_uint64)]
@@ -99,6 +111,9 @@ SYMBOLS = {
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
     "krea_cuda_gemm": (_int, [_vp, ctypes.POINTER(GemmArgs)]),
+    "krea_cuda_rms_norm": (_int, [_vp, ctypes.POINTER(RmsNormArgs)]),
+    "krea_cuda_dit_block_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(DitBlockArgs)]),
+    "krea_cuda_dit_block": (_int, [_vp, ctypes.POINTER(DitBlockArgs)]),
     "krea_cuda_layerwise_attn": (_int, [_vp, ctypes.POINTER(LayerwiseArgs)]),
     "krea_cuda_qw_open": (_vp, [ctypes.c_char_p, ctypes.c_char_p, _int]),
     "krea_cuda_qw_close": (None, [_vp]),

@@ -108,6 +108,19 @@ struct LayerwiseParams {
 };
 cudaError_t launch_layerwise_attn(const LayerwiseParams& p, cudaStream_t stream);
 
+// Row-wise RMSNorm of fp32 rows with per-column multiplier / addend (rms_norm.cu).
+struct RmsNormParams {
+  const float* x;
+  const float* mul;
+  const float* add;   // nullptr = none
+  void* y;            // bf16 or fp32
+  int rows, width;
+  int64_t ld_in, ld_out;
+  float eps;
+  int f32_out;
+};
+cudaError_t launch_rms_norm(const RmsNormParams& p, cudaStream_t stream);
+
 // bf16 GEMM C = A x Wt with optional fused QK-norm + RoPE epilogue (gemm_sm100.cu).  Strides in elements.
 struct GemmParams {
   __nv_bfloat16* C;

@@ -45,6 +45,8 @@ struct krea_cuda {
   std::vector<cudaEvent_t> event_pool;
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
   int sm_count = 0;                 // SMs of the device (persistent kernels size their grid by it)
+  void* block_ws = nullptr;         // intermediates of krea_cuda_dit_block when the caller passes no workspace
+  size_t block_ws_bytes = 0;
   void* qw_stage = nullptr;         // pinned staging of krea_cuda_qw_upload (two 8 MiB halves)
 };
 

@@ -99,6 +99,7 @@ void krea_cuda_destroy(krea_cuda* h) {
     if (h->pipe_ev[i]) cudaEventDestroy(h->pipe_ev[i]);
   if (h->bounce) cudaFreeHost(h->bounce);
   if (h->qw_stage) cudaFreeHost(h->qw_stage);
+  if (h->block_ws) cudaFree(h->block_ws);
   if (h->copy_in) cudaStreamDestroy(h->copy_in);
   if (h->copy_out) cudaStreamDestroy(h->copy_out);
   if (h->own_stream) cudaStreamDestroy(h->own_stream);
@@ -765,6 +766,118 @@ int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) {
   CUDA_TRY(h, launch_gemm_bf16_sm100(tmA, tmW, p, h->sm_count, h->stream));
   h->launches++;
   return KREA_CUDA_OK;
+}
+
+int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "rms_norm: null handle or arguments");
+  if (a->rows < 0 || a->width < 0) return fail(h, KREA_CUDA_E_ARG, "rms_norm: negative size");
+  if (a->rows == 0 || a->width == 0) return KREA_CUDA_OK;
+  if (!a->x || !a->mul || !a->y || !aligned16(a->x) || !aligned16(a->mul) || !aligned16(a->add) || !aligned16(a->y))
+    return fail(h, KREA_CUDA_E_ARG, "rms_norm: null or misaligned pointer");
+  const int m = a->f32_out ? 4 : 8;
+  if (a->width % 4 || a->ld_in % 4 || a->ld_out % m || a->ld_in < a->width || a->ld_out < a->width)
+    return fail(h, KREA_CUDA_E_ARG, "rms_norm: width and leading dimensions must be multiples of 4 (8 for the bf16 output) and cover the row");
+  RmsNormParams p{};
+  p.x = a->x; p.mul = a->mul; p.add = a->add; p.y = a->y;
+  p.rows = a->rows; p.width = a->width; p.ld_in = a->ld_in; p.ld_out = a->ld_out;
+  p.eps = a->eps; p.f32_out = a->f32_out ? 1 : 0;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, launch_rms_norm(p, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+
+// byte offsets of the block's intermediates inside its workspace: h | qkvg | ao | mid
+struct BlockLayout {
+  size_t h, qkvg, ao, mid, total;
+  int dim, qkvg_cols;
+};
+static BlockLayout block_layout(const krea_cuda_dit_block_args* a) {
+  BlockLayout l{};
+  l.dim = a->heads * 128;
+  l.qkvg_cols = (2 * a->heads + 2 * a->kv_heads) * 128;
+  auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  const size_t rows = (size_t)(a->rows > 0 ? a->rows : 0);
+  l.h = 0;
+  l.qkvg = l.h + up(rows * l.dim * 2);
+  l.ao = l.qkvg + up(rows * l.qkvg_cols * 2);
+  l.mid = l.ao + up(rows * l.dim * 2);
+  l.total = l.mid + up(rows * (size_t)(a->ff > 0 ? a->ff : 0) * 2);
+  return l;
+}
+
+size_t krea_cuda_dit_block_workspace_bytes(const krea_cuda_dit_block_args* a) {
+  if (!a || a->rows <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->ff <= 0) return 0;
+  return block_layout(a).total;
+}
+
+int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "dit_block: null handle or arguments");
+  if (a->rows < 0 || a->heads <= 0 || a->kv_heads <= 0 || a->ff <= 0 || a->heads % a->kv_heads) return fail(h, KREA_CUDA_E_ARG, "dit_block: bad sizes");
+  if (a->ff % 32) return fail(h, KREA_CUDA_E_ARG, "dit_block: ff must be a multiple of 32 (gate / up interleave)");
+  if (a->rows == 0) return KREA_CUDA_OK;
+  if (!a->x || !a->mods || !a->w_qkvg || !a->w_o || !a->w_gu || !a->w_down || !a->qn || !a->kn || !a->cos || !a->sin)
+    return fail(h, KREA_CUDA_E_ARG, "dit_block: null tensor");
+  const BlockLayout l = block_layout(a);
+  char* ws = (char*)a->workspace;
+  if (ws) {
+    if (a->workspace_bytes < l.total || !aligned16(ws)) return fail(h, KREA_CUDA_E_NOMEM, "dit_block: workspace too small (%zu < %zu) or misaligned", a->workspace_bytes, l.total);
+  } else {
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    if (h->block_ws_bytes < l.total) {
+      CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+      if (h->block_ws) cudaFree(h->block_ws);
+      h->block_ws = nullptr;
+      h->block_ws_bytes = 0;
+      if (cudaMalloc(&h->block_ws, l.total) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, KREA_CUDA_E_NOMEM, "dit_block: cannot allocate %zu bytes of workspace", l.total);
+      }
+      h->block_ws_bytes = l.total;
+    }
+    ws = (char*)h->block_ws;
+  }
+  const int D = l.dim, QC = l.qkvg_cols, R = a->rows, H = a->heads, KV = a->kv_heads;
+  const float* mod = a->mods;
+  void* hb = ws + l.h;
+  char* qkvg = ws + l.qkvg;
+  void* ao = ws + l.ao;
+  void* mid = ws + l.mid;
+  int rc;
+  // 1. h = rms_norm(x) * mul1 + add1                                           (model.mm:373)
+  krea_cuda_rmsnorm_args n1 = {a->x, mod, mod + D, hb, R, D, D, D, a->eps, 0};
+  if ((rc = krea_cuda_rms_norm(h, &n1))) return rc;
+  // 2. q | k | v | gate = h Wqkvg, q and k normalised and rotated in the epilogue  (model.mm:374-375)
+  krea_cuda_gemm_args g1 = {};
+  g1.A = hb; g1.W = a->w_qkvg; g1.C = qkvg; g1.M = R; g1.N = QC; g1.K = D; g1.lda = D; g1.ldw = QC; g1.ldc = QC;
+  g1.epilogue = KREA_CUDA_EPI_QKNORM_ROPE;
+  g1.q_off = 0; g1.n_q = H; g1.k_off = D; g1.n_k = KV;
+  g1.wq = a->qn; g1.wk = a->kn; g1.cos = a->cos; g1.sin = a->sin; g1.row0 = 0; g1.eps = a->eps; g1.rope_mode = KREA_CUDA_ROPE_PAIRS;
+  if ((rc = krea_cuda_gemm(h, &g1))) return rc;
+  // 3. ao = attention(q, k, v) * sigmoid(gate)                                  (model.mm:282-288, 377)
+  krea_cuda_attn_args at = {};
+  at.Q = qkvg; at.K = qkvg + (size_t)D * 2; at.V = qkvg + (size_t)(D + KV * 128) * 2; at.O = ao;
+  at.Lq = R; at.Lk = R; at.heads = H; at.ldq = QC; at.ldk = QC; at.ldv = QC; at.ldo = D; at.group = H / KV;
+  at.G = qkvg + (size_t)(D + 2 * KV * 128) * 2; at.ldg = QC;
+  at.batch = 1;
+  if ((rc = krea_cuda_attention(h, &at))) return rc;
+  // 4. x += gate1 * (ao Wo)                                                     (model.mm:357-359, 379)
+  krea_cuda_gemm_args g2 = {};
+  g2.A = ao; g2.W = a->w_o; g2.C = a->x; g2.M = R; g2.N = D; g2.K = D; g2.lda = D; g2.ldw = D; g2.ldc = D;
+  g2.epilogue = KREA_CUDA_EPI_RESID_GATE; g2.vec = mod + 2 * (size_t)D;
+  if ((rc = krea_cuda_gemm(h, &g2))) return rc;
+  // 5. h = rms_norm(x) * mul2 + add2                                           (model.mm:381)
+  krea_cuda_rmsnorm_args n2 = {a->x, mod + 3 * (size_t)D, mod + 4 * (size_t)D, hb, R, D, D, D, a->eps, 0};
+  if ((rc = krea_cuda_rms_norm(h, &n2))) return rc;
+  // 6. mid = swiglu(h Wgu);  7. x += gate2 * (mid Wdown)                       (model.mm:361-366, 382)
+  krea_cuda_gemm_args g3 = {};
+  g3.A = hb; g3.W = a->w_gu; g3.C = mid; g3.M = R; g3.N = 2 * a->ff; g3.K = D; g3.lda = D; g3.ldw = 2 * a->ff; g3.ldc = a->ff;
+  g3.epilogue = KREA_CUDA_EPI_SWIGLU;
+  if ((rc = krea_cuda_gemm(h, &g3))) return rc;
+  krea_cuda_gemm_args g4 = {};
+  g4.A = mid; g4.W = a->w_down; g4.C = a->x; g4.M = R; g4.N = D; g4.K = a->ff; g4.lda = a->ff; g4.ldw = D; g4.ldc = D;
+  g4.epilogue = KREA_CUDA_EPI_RESID_GATE; g4.vec = mod + 5 * (size_t)D;
+  return krea_cuda_gemm(h, &g4);
 }
 
 int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwise_args* a) {

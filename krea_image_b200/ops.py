@@ -153,6 +153,18 @@ class KreaCuda:
             a.row0, a.eps, a.rope_mode = qk_norm.get("row0", 0), qk_norm.get("eps", 1e-6), qk_norm.get("rope_mode", B.ROPE_PAIRS)
         self._check(self.lib.krea_cuda_gemm(self.h, ctypes.byref(a)))
 
+    def rms_norm(self, x, mul, add, y, rows, width, ld_in, ld_out, eps, f32_out=False):
+        """Metal::rms_norm (engine/src/metal.h:75-77): same argument order."""
+        a = B.RmsNormArgs(_ptr(x), _ptr(mul), _ptr(add), _ptr(y), rows, width, ld_in, ld_out, eps, int(bool(f32_out)))
+        self._check(self.lib.krea_cuda_rms_norm(self.h, ctypes.byref(a)))
+
+    def dit_block(self, x, mods, w_qkvg, w_o, w_gu, w_down, qn, kn, cos, sin, rows, heads, kv_heads, ff, eps=1e-6, workspace=None):
+        """DiT::layer (engine/src/model.mm:369-385) on the fp32 residual stream x [rows, heads*128], in place."""
+        a = B.DitBlockArgs(_ptr(x), _ptr(mods), _ptr(w_qkvg), _ptr(w_o), _ptr(w_gu), _ptr(w_down), _ptr(qn), _ptr(kn),
+                           _ptr(cos), _ptr(sin), rows, heads, kv_heads, ff, eps, _ptr(workspace),
+                           0 if workspace is None else workspace.numel() * workspace.element_size())
+        self._check(self.lib.krea_cuda_dit_block(self.h, ctypes.byref(a)))
+
     def layerwise_attn(self, qkvg, out, rows, ld, ldo, heads, q_off, k_off, v_off, g_off):
         """Metal::layerwise_attn (engine/src/metal.h:90-91): same argument order."""
         a = B.LayerwiseArgs(_ptr(qkvg), _ptr(out), rows, ld, ldo, heads, q_off, k_off, v_off, g_off)

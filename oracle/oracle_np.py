@@ -92,3 +92,39 @@ def layerwise_attn(qkvg_bits, rows, ld, heads, q_off, k_off, v_off, g_off):
     p /= p.sum(axis=-1, keepdims=True)
     o = np.einsum("thij,tjhd->tihd", p, v) / (1.0 + np.exp(-g))
     return o.reshape(rows, heads * 128)
+
+
+def rms_norm(x, mul, add, eps):
+    """Metal::rms_norm (norm.metal:28-55): x [rows, width] float64."""
+    r = 1.0 / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
+    y = x * r * mul
+    return y if add is None else y + add
+
+
+def dit_block(x, mods, w_qkvg, w_o, w_gu, w_down, qn, kn, cos, sin, heads, kv_heads, ff, eps=1e-6, ref_rounding=False):
+    """DiT::layer (model.mm:369-385) in float64.  x [rows, heads*128]; mods [6, dim]; weights [K, N] as float64
+    (already widened from bf16).  ref_rounding rounds to bf16 wherever the reference stores bf16: the normalised
+    rows, the projection, q and k after the norm, P inside P V, the attention output, the SwiGLU output."""
+    R = round_bf16 if ref_rounding else (lambda a: a)
+    D = heads * 128
+    group = heads // kv_heads
+    x = np.array(x, dtype=np.float64)
+    h = R(rms_norm(x, mods[0], mods[1], eps))
+    y = R(h @ w_qkvg)
+    S = x.shape[0]
+    q = y[:, :D].reshape(S, heads, 128).transpose(1, 0, 2)
+    k = y[:, D:D + kv_heads * 128].reshape(S, kv_heads, 128).transpose(1, 0, 2)
+    v = y[:, D + kv_heads * 128:D + 2 * kv_heads * 128].reshape(S, kv_heads, 128).transpose(1, 0, 2)
+    g = y[:, D + 2 * kv_heads * 128:].reshape(S, heads, 128).transpose(1, 0, 2)
+    q = R(norm_rope(q, qn, cos, sin, eps, 0))
+    k = R(norm_rope(k, kn, cos, sin, eps, 0))
+    ao = np.empty((S, heads, 128))
+    for hh in range(heads):
+        o = attention_core(q[hh], k[hh // group], v[hh // group], round_p=ref_rounding)
+        ao[:, hh] = o / (1.0 + np.exp(-g[hh]))
+    ao = R(ao.reshape(S, D))
+    x = x + mods[2] * (ao @ w_o)
+    h = R(rms_norm(x, mods[3], mods[4], eps))
+    z = (h @ w_gu).reshape(S, 2 * ff // 64, 2, 32)              # groups of 64 columns: 32 gate, then 32 up
+    mid = R((z[:, :, 0] / (1.0 + np.exp(-z[:, :, 0])) * z[:, :, 1]).reshape(S, ff))
+    return x + mods[5] * (mid @ w_down)

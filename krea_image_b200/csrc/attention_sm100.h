@@ -140,6 +140,7 @@ struct GemmParams {
   uint32_t* status;
 };
 // A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.
-cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream);
+// force_bn: 0 = choose the tile width (256 or 128 columns) by how well the tiles fill the last wave; 128 / 256 = as told
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, int force_bn, cudaStream_t stream);
 
 }  // namespace krea

@@ -8,7 +8,7 @@
 // pass over them disappears.
 //
 // Shares nothing with the reference's simdgroup kernels:
-//   * persistent CTAs walk 128 x 256 output tiles; one warp issues TMA loads of A (K-major) and Wt (N-major,
+//   * persistent CTAs walk 128 x 256 output tiles (128 x 128 when that fills the last wave of CTAs better); one warp issues TMA loads of A (K-major) and Wt (N-major,
 //     exactly as it lies in memory) into a 4-stage ring of 128B-swizzled shared memory, one warp issues
 //     tcgen05.mma (M128 N256 K16) into one of two 256-column accumulators in tensor memory, four warps
 //     drain the other accumulator - the epilogue of tile i overlaps the main loop of tile i + 1;
@@ -26,20 +26,29 @@
 namespace krea {
 
 namespace gemm {
-constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
+constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB: [128 rows][64 k], K-major
-constexpr int B_BYTES = BK * BN * 2;          // 32 KB: four blocks of [64 k][64 n], N-major
-constexpr int B_BLOCK = BK * 64 * 2;          // 8 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int B_BLOCK = BK * 64 * 2;          // 8 KB: [64 k][64 n], N-major
 constexpr int THREADS = 256;                  // warp 0 TMA, warp 1 MMA, warps 4-7 epilogue
-constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
 enum : uint32_t { SITE_FULL = 11, SITE_EMPTY = 12, SITE_ACC_FULL = 13, SITE_ACC_EMPTY = 14 };
+// Tile width: 256 columns halve the A traffic per flop; 128 columns give twice as many tiles, which matters
+// when the 256-wide tiles would leave the last wave of the 148 CTAs mostly idle.
+template <int BN_>
+struct Cfg {
+  static constexpr int BN = BN_;
+  static constexpr int B_BYTES = BK * BN * 2;                 // BN / 64 blocks
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KB or 32 KB
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
+};
 }  // namespace gemm
 
+template <int BN>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
   using namespace gemm;
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -67,7 +76,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -75,8 +84,19 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile t -> (m tile, n tile): m fastest, so the CTAs running together share a few column blocks of Wt
-  // (read from HBM once) while A stays in L2
+  // tile t -> (m tile, n tile): tiles are dealt out in groups of GROUP_M row blocks x all column blocks, row
+  // block fastest inside a group.  The CTAs running together then share ~16 row blocks of A and ~9 column
+  // blocks of Wt, a group's slice of A (a few MB) stays in L2 for the whole group, and with many row blocks A is
+  // not streamed through L2 once per column block.
+  constexpr int GROUP_M = 16;
+  auto tile_origin = [&](int t, int& m0, int& n0) {
+    const int per_group = GROUP_M * nt;
+    const int g = t / per_group, first = g * GROUP_M;
+    const int gm = min(GROUP_M, mt - first);
+    const int local = t - g * per_group;
+    m0 = (first + local % gm) * BM;
+    n0 = (local / gm) * BN;
+  };
   if (warp == 0) {
     // ======================================= TMA producer =======================================
     if (lane == 0) {
@@ -84,7 +104,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tma_prefetch_desc(&tmW);
       uint32_t n = 0;     // k-blocks issued so far
       for (int t = blockIdx.x; t < tiles && *abort_word == 0u; t += gridDim.x) {
-        const int m0 = (t % mt) * BM, n0 = (t / mt) * BN;
+        int m0, n0;
+        tile_origin(t, m0, n0);
         for (int kb = 0; kb < kblocks; kb++, n++) {
           const int s = n % STAGES;
           if (!mbar_wait(&empty[s], ((n / STAGES) & 1) ^ 1, abort_word, SITE_EMPTY)) break;
@@ -147,7 +168,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int it = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
       const int a = it & 1;
-      const int m0 = (t % mt) * BM, n0 = (t / mt) * BN;
+      int m0, n0;
+      tile_origin(t, m0, n0);
       if (!mbar_wait(&acc_full[a], (it >> 1) & 1, abort_word, SITE_ACC_FULL)) break;
       tc_fence_after();
       const int row = m0 + r;
@@ -279,7 +301,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, 2 * BN);
   }
   if (threadIdx.x == 0 && p.status != nullptr) {
     const uint32_t a = *abort_word;
@@ -287,21 +309,34 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
-cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream) {
+template <int BN>
+static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream) {
   using namespace gemm;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  if (tiles <= 0 || p.K <= 0) return cudaSuccess;
   const int grid = tiles < sms ? tiles : sms;
-  gemm_bf16_sm100<<<grid, THREADS, SMEM, stream>>>(tmA, tmW, p);
+  gemm_bf16_sm100<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(tmA, tmW, p);
   return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, int force_bn, cudaStream_t stream) {
+  using namespace gemm;
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) return cudaSuccess;
+  // share of the CTAs' time slots that do work when the tiles are dealt out in waves of `sms`
+  auto wave_eff = [&](int bn) {
+    const long long tiles = (long long)((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    return (double)tiles / (double)(waves * sms);
+  };
+  const bool narrow = force_bn == 128 || (force_bn != 256 && wave_eff(128) > wave_eff(256) * 1.05);
+  return narrow ? launch_gemm_variant<128>(tmA, tmW, p, sms, stream) : launch_gemm_variant<256>(tmA, tmW, p, sms, stream);
 }
 
 }  // namespace krea

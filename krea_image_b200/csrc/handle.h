@@ -44,6 +44,7 @@ struct krea_cuda {
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[4];   // pending (start, stop) pairs per kind of work
   std::vector<cudaEvent_t> event_pool;
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
+  int gemm_bn = 0;                  // GEMM tile width: 0 = chosen per problem, 128 or 256 = forced
   int sm_count = 0;                 // SMs of the device (persistent kernels size their grid by it)
   void* block_ws = nullptr;         // intermediates of krea_cuda_dit_block when the caller passes no workspace
   size_t block_ws_bytes = 0;

@@ -72,6 +72,10 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
   if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_O_TMA")) h->o_tma = atoi(s) != 0;                 // tuning knob
+  if (const char* s = getenv("KREA_CUDA_GEMM_BN")) {                                      // tuning knob: GEMM tile width
+    const int v = atoi(s);
+    if (v == 128 || v == 256) h->gemm_bn = v;
+  }
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);
     if (v >= 0 && v <= 1) h->emu = v;
@@ -763,7 +767,7 @@ int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) {
     CUDA_TRY(h, cudaGetDeviceProperties(&prop, h->device));
     h->sm_count = prop.multiProcessorCount;
   }
-  CUDA_TRY(h, launch_gemm_bf16_sm100(tmA, tmW, p, h->sm_count, h->stream));
+  CUDA_TRY(h, launch_gemm_bf16_sm100(tmA, tmW, p, h->sm_count, h->gemm_bn, h->stream));
   h->launches++;
   return KREA_CUDA_OK;
 }

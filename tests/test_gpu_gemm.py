@@ -139,6 +139,29 @@ def test_gemm_swiglu_epilogue(kc):
         kc.gemm(_dev(a), _dev(w), c, M, N - 32, K, K, N, H1 + 8, epilogue=binding.EPI_SWIGLU)   # not a whole number of groups
 
 
+def test_gemm_tile_width_variants(monkeypatch):
+    """The two tile widths (128 x 256 and 128 x 128, chosen per problem by how the tiles fill the CTAs' last wave)
+    accumulate every output element in the same order: forced either way, the results are bit-identical."""
+    M, N, K = 300, 1000, 328
+    a, w = _case(41, M, N, K, K, N)
+    outs = []
+    for bn in ("128", "256"):
+        monkeypatch.setenv("KREA_CUDA_GEMM_BN", bn)
+        k2 = ops.KreaCuda(0)
+        try:
+            k2.set_stream(torch.cuda.current_stream())
+            c = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+            k2.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N)
+            k2.wait()
+            outs.append(c)
+        finally:
+            k2.close()
+    assert torch.equal(outs[0], outs[1])
+    want = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+    rel, _ = _rel(outs[0].float().cpu().numpy(), want)
+    assert rel <= 3e-3
+
+
 def test_gemm_model_size_projection(kc):
     """The q|k|v projection at the headline configuration's size (4608 x 9216 x 3072) against float32 numpy."""
     M, N, K = 4608, 9216, 3072

@@ -104,3 +104,31 @@ def big_dim(qn: np.ndarray, kn: np.ndarray, gain_threshold: float = 256.0) -> in
     kn = np.ascontiguousarray(kn, dtype=np.float32)
     assert qn.size == 128 and kn.size == 128
     return int(B.load().krea_cuda_qw_big_dim(qn.ctypes.data, kn.ctypes.data, ctypes.c_float(gain_threshold)))
+
+
+class BlockWeights:
+    """One DiT layer's tensors (`L<l>.qkvg`, `.o`, `.gu`, `.down` bf16 [K, N]; `.qn`, `.kn` f32 [128]) on the
+    device: the layer's whole segment of the file is uploaded as one byte range (its tensors are contiguous
+    in the file, weights.h:17-22) and the tensors are views into that buffer."""
+
+    NAMES = ("qkvg", "o", "gu", "down", "qn", "kn")
+
+    def __init__(self, kc, wf: WeightFile, layer: int):
+        import torch
+        prefix = f"L{layer}."
+        off, length = wf.span(prefix)
+        self.segment = torch.empty(length, dtype=torch.uint8, device=f"cuda:{kc.device}")
+        wf.upload(kc, off, length, self.segment)
+        self.info = {}
+        for n in self.NAMES:
+            ti = wf.info(prefix + n)
+            view = self.segment[ti.offset - off:ti.offset - off + ti.nbytes]
+            self.info[n] = ti
+            setattr(self, n, view.view(torch.bfloat16 if ti.dtype == "bf16" else torch.float32).view(ti.shape))
+        if self.qkvg.dtype != torch.bfloat16:
+            raise ValueError("only bf16 weights are supported (the file holds int8 weights with group scales)")
+
+    def run(self, kc, x, mods, cos, sin, rows, heads, kv_heads, eps=1e-6):
+        """DiT::layer on the residual stream x with this layer's weights."""
+        ff = self.info["down"].shape[0]
+        kc.dit_block(x, mods, self.qkvg, self.o, self.gu, self.down, self.qn, self.kn, cos, sin, rows, heads, kv_heads, ff, eps)

@@ -142,3 +142,47 @@ def test_weights_from_file_feed_the_fused_attention(tmp_path):
         assert rel <= 5e-3 and np.abs(got - want[0]).max() <= 2e-2
     finally:
         kc.close()
+
+
+@pytest.mark.gpu
+def test_block_weights_from_file_drive_the_dit_block(tmp_path):
+    """A converter-style file (tools/convert.py:196-213: qkvg = q|k|v|gate, gu interleaved, all [K, N] bf16) ->
+    one segment upload -> krea_cuda_dit_block: same bits as the block run on separately uploaded tensors."""
+    import torch
+
+    from krea_image_b200 import ops
+    rng = np.random.default_rng(12)
+    heads, kv, ff, T, gh, gw = 2, 1, 256, 16, 6, 8
+    D, S = heads * 128, T + gh * gw
+    QC = (2 * heads + 2 * kv) * 128
+    bf = lambda a: synth.f32_to_bf16_bits(np.ascontiguousarray(a, dtype=np.float32)).reshape(a.shape)
+    ts = []
+    for l in range(2):
+        ts += [(f"L{l}.qkvg", "bf16", bf(rng.standard_normal((D, QC)) / np.sqrt(D))), (f"L{l}.o", "bf16", bf(rng.standard_normal((D, D)) / np.sqrt(D))),
+               (f"L{l}.gu", "bf16", bf(rng.standard_normal((D, 2 * ff)) / np.sqrt(D))), (f"L{l}.down", "bf16", bf(rng.standard_normal((ff, D)) / np.sqrt(ff))),
+               (f"L{l}.qn", "f32", rng.uniform(0.5, 1.5, 128).astype(np.float32)), (f"L{l}.kn", "f32", rng.uniform(0.5, 1.5, 128).astype(np.float32)),
+               (f"L{l}.n1", "f32", np.ones(D, np.float32))]
+    path = tmp_path / "dit.qw"
+    write_qw(path, ts, meta={"model": "krea2-turbo-dit", "layers": 2, "q8": False})
+    x0 = rng.standard_normal((S, D)).astype(np.float32)
+    mods = (1.0 + 0.1 * rng.standard_normal((6, D))).astype(np.float32)
+    cos, sin = synth.rope_tables_axial2d(T, gh, gw)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    kc = ops.KreaCuda(0)
+    kc.set_stream(torch.cuda.current_stream())
+    try:
+        with weights.WeightFile(path) as w:
+            assert w.meta()["q8"] is False
+            bw = weights.BlockWeights(kc, w, 1)
+            x = dev(x0)
+            bw.run(kc, x, dev(mods), dev(cos), dev(sin), S, heads, kv)
+            kc.wait()
+            t = {n: a for n, _, a in ts}
+            tb = lambda n: torch.from_numpy(t[n].view(np.int16)).cuda().view(torch.bfloat16)
+            x2 = dev(x0)
+            kc.dit_block(x2, dev(mods), tb("L1.qkvg"), tb("L1.o"), tb("L1.gu"), tb("L1.down"), dev(t["L1.qn"]), dev(t["L1.kn"]), dev(cos), dev(sin),
+                         S, heads, kv, ff)
+            kc.wait()
+            assert torch.equal(x, x2) and bool(torch.isfinite(x).all()) and not torch.equal(x, dev(x0))
+    finally:
+        kc.close()

@@ -115,6 +115,9 @@ def run_reference(args, rank, world):
     reference itself is Metal-only), timed with every host thread on a bounded sample per step."""
     if rank != 0:
         return
+    if args.workload == "block":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's block runs on Metal only (unavailable on this box); its CPU restatement is a numpy statement sized for tests"}))
+        return
     import oracle
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
     heads_sel = list(range(0, cfg.heads, 6))          # 4 of 24 heads per step
@@ -243,6 +246,86 @@ def run_seq_parallel(args, rank, world, local_rank):
     kc.close()
 
 
+def run_block(args, rank, world, local_rank):
+    """--workload block: one whole DiT block (DiT::layer, engine/src/model.mm:369-385) at the reference model's
+    width - dim 6144, 48 query / 12 key-value heads, FF 16384 - on the 4608 rows of a 1024^2 image, bf16 weights
+    with random values.  Every GPU runs its own block (weak scaling; the block has no multi-GPU form here)."""
+    import torch
+    import torch.distributed as dist
+
+    from krea_image_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    heads, kv, ff, S = 48, 12, 16384, 4608
+    D, QC = heads * 128, (2 * heads + 2 * kv) * 128
+    kc = ops.KreaCuda(local_rank)
+    stream = torch.cuda.current_stream()
+    kc.set_stream(stream)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    W = lambda a, b: (torch.randn(a, b, device="cuda", generator=g) / a ** 0.5).to(torch.bfloat16)
+    wqkvg, wo, wgu, wdown = W(D, QC), W(D, D), W(D, 2 * ff), W(ff, D)
+    x = torch.randn(S, D, device="cuda", generator=g)
+    mods = torch.randn(6, D, device="cuda", generator=g) * 0.1
+    mods[0] += 1
+    mods[3] += 1
+    qn = torch.rand(128, device="cuda", generator=g) + 0.5
+    kn = torch.rand(128, device="cuda", generator=g) + 0.5
+    cos_h, sin_h = ops.rope_tables_axial2d(512, 64, 64)
+    cos, sin = torch.from_numpy(cos_h).cuda(), torch.from_numpy(sin_h).cuda()
+    x0 = x.clone()
+
+    def step():
+        x.copy_(x0)                      # keep the stream's values bounded over many steps (151 MB copy, ~2 % of a step)
+        kc.dit_block(x, mods, wqkvg, wo, wgu, wdown, qn, kn, cos, sin, S, heads, kv, ff)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    kc.wait()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    n0 = kc.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    launches = kc.launches - n0
+    kc.wait()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, peak_sustained, peak_kind = measured_peaks()
+        gemm_flops = 2.0 * S * (D * QC + D * D + D * 2 * ff + ff * D)
+        attn_flops = 4.0 * 128 * heads * float(S) ** 2
+        value = world * (gemm_flops + attn_flops) / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "DiT block TFLOP/s at 4608 rows (1024^2), dim 6144, 48/12 heads, FF 16384", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "dit-block-1024sq", "rows": S, "dim": D, "heads": heads, "kv_heads": kv, "ff": ff,
+                       "flops_per_step_per_gpu": gemm_flops + attn_flops, "gemm_flops": gemm_flops, "attention_flops": attn_flops,
+                       "l2": "weights (868 MB) and activations exceed the 126 MB L2"},
+            "pct_of_measured_bf16_peak": 100.0 * value / world / peak, "gpu_launches": int(launches), "clocks": clocks,
+            "e2e": None,
+            "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s", "frac": value / world / peak_sustained,
+                         "traffic": None, "peak_kind": f"{peak_kind} sustained bf16 GEMM (a step is several ms of tensor work under the power cap)",
+                         "kernel": "whole block: 4 x gemm_bf16_sm100, attn_fwd_sm100, 2 x rms_norm_kernel"}}))
+    kc.close()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -251,6 +334,8 @@ def run_ours(args, rank, world, local_rank):
 
     if args.workload == "c4":
         return run_seq_parallel(args, rank, world, local_rank)
+    if args.workload == "block":
+        return run_block(args, rank, world, local_rank)
     torch.cuda.set_device(local_rank)
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
     B, S, H = cfg.batch, cfg.seq, cfg.heads
@@ -397,7 +482,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["block"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--shard", default="samples", choices=["samples", "heads"],
                     help="several GPUs, workloads c0-c3: every GPU runs a whole problem (weak scaling), or its share of the heads of one problem (strong)")

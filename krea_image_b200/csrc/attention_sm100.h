@@ -137,6 +137,10 @@ struct GemmParams {
   int row0;                     // table row of output row 0
   float eps;
   int rope_mode;                // 0 interleaved pairs, 2 none
+  // epi 1, optional: one CTA also writes the a-priori bound on |q'.k'| * scale * log2(e) that the QK-norm
+  // weights imply (128 * max|wq| * max|wk|, 2 % head-room), for the attention kernel's bounded softmax
+  float* bound_out;
+  float bound_scale_log2;
   uint32_t* status;
 };
 // A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.

@@ -244,6 +244,7 @@ struct AttnCall {
   int causal, q_pos0;
   const float *QB, *KB;
   bool pdl;             // programmatic dependent launch after the K pre-pass (fused call only)
+  bool bound_given;     // logit_bound holds for Q and K as they are (normalised by an earlier kernel)
   void* const* o_blk;   // row-block scatter of the output (see AttnParams::O_blk), nullptr = none
   int o_blk_n, o_blk_rows;
 };
@@ -279,7 +280,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.QB = c.QB; p.KB = c.KB; p.ldqb = c.heads; p.ldkb = kvheads;      // row strides = heads and heads / group (metal.h:85)
   p.wq = c.wq; p.cos = c.cos; p.sin = c.sin; p.eps = c.eps; p.rope_mode = c.rope_mode; p.q_row0 = c.q_row0;
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
-  p.logit_bound = (h->static_bound && c.wq) ? c.logit_bound : nullptr;
+  p.logit_bound = (h->static_bound && (c.wq || c.bound_given)) ? c.logit_bound : nullptr;
   p.status = h->status_dev;
   p.pdl = c.pdl ? 1 : 0;
   if (c.o_blk != nullptr) {
@@ -725,7 +726,8 @@ static int reshard(krea_cuda* h, const krea_cuda_reshard_args* a, bool unpack) {
   h->launches++;
   return KREA_CUDA_OK;
 }
-int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) {
+// bound_out: with the fused QK-norm epilogue, where the kernel leaves the logit bound its weights imply (or nullptr)
+static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_out) {
   if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "gemm: null handle or arguments");
   if (a->M < 0 || a->N < 0 || a->K < 0) return fail(h, KREA_CUDA_E_ARG, "gemm: negative size");
   if (a->M == 0 || a->N == 0) return KREA_CUDA_OK;
@@ -756,6 +758,10 @@ int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) {
     p.q_off = a->q_off; p.n_q = a->n_q; p.k_off = a->k_off; p.n_k = a->n_k;
     p.wq = a->wq ? a->wq : a->wk; p.wk = a->wk ? a->wk : a->wq;
     p.cos = a->cos; p.sin = a->sin; p.row0 = a->row0; p.eps = a->eps; p.rope_mode = a->rope_mode;
+    if (bound_out && a->n_q > 0 && a->n_k > 0) {
+      p.bound_out = bound_out;
+      p.bound_scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);
+    }
   }
   CUDA_TRY(h, cudaSetDevice(h->device));
   CUtensorMap tmA, tmW;
@@ -771,6 +777,8 @@ int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) {
   h->launches++;
   return KREA_CUDA_OK;
 }
+
+int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) { return gemm_impl(h, a, nullptr); }
 
 int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args* a) {
   if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "rms_norm: null handle or arguments");
@@ -857,14 +865,19 @@ int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a) {
   g1.epilogue = KREA_CUDA_EPI_QKNORM_ROPE;
   g1.q_off = 0; g1.n_q = H; g1.k_off = D; g1.n_k = KV;
   g1.wq = a->qn; g1.wk = a->kn; g1.cos = a->cos; g1.sin = a->sin; g1.row0 = 0; g1.eps = a->eps; g1.rope_mode = KREA_CUDA_ROPE_PAIRS;
-  if ((rc = krea_cuda_gemm(h, &g1))) return rc;
+  float* bound = (float*)(h->status_dev + 8);         // the device float the fused call's pre-pass uses too
+  if ((rc = gemm_impl(h, &g1, bound))) return rc;
   // 3. ao = attention(q, k, v) * sigmoid(gate)                                  (model.mm:282-288, 377)
-  krea_cuda_attn_args at = {};
+  // Q and K arrive normalised, so the operator runs without its prologue - but with the logit bound the
+  // projection's epilogue derived from the QK-norm weights, i.e. with the bounded form of the softmax.
+  AttnCall at{};
   at.Q = qkvg; at.K = qkvg + (size_t)D * 2; at.V = qkvg + (size_t)(D + KV * 128) * 2; at.O = ao;
-  at.Lq = R; at.Lk = R; at.heads = H; at.ldq = QC; at.ldk = QC; at.ldv = QC; at.ldo = D; at.group = H / KV;
-  at.G = qkvg + (size_t)(D + 2 * KV * 128) * 2; at.ldg = QC;
-  at.batch = 1;
-  if ((rc = krea_cuda_attention(h, &at))) return rc;
+  at.G = qkvg + (size_t)(D + 2 * KV * 128) * 2;
+  at.batch = 1; at.Lq = R; at.Lk = R; at.heads = H; at.group = H / KV;
+  at.ldq = QC; at.ldk = QC; at.ldv = QC; at.ldo = D; at.ldg = QC;
+  at.logit_bound = bound;
+  at.bound_given = true;
+  if ((rc = run_attention(h, at))) return rc;
   // 4. x += gate1 * (ao Wo)                                                     (model.mm:357-359, 379)
   krea_cuda_gemm_args g2 = {};
   g2.A = ao; g2.W = a->w_o; g2.C = a->x; g2.M = R; g2.N = D; g2.K = D; g2.lda = D; g2.ldw = D; g2.ldc = D;

@@ -243,6 +243,12 @@ typedef struct {
   float eps;
   int rope_mode;
   const float* vec;   /* RESID_GATE: per-column gate, f32 [N] (the reference's `vec` argument) */
+  /* QKNORM_ROPE, optional (qk_norm_rope's big_dim, norm.metal:127-132): when qbig and kbig are given, head
+   * dimension big_dim of every Q / K head is written to qbig [M, n_q] / kbig [M, n_k] in fp32 and stored as
+   * zero in C, for the attention's QB / KB term.  NULL = off (big_dim ignored). */
+  int big_dim;
+  float* qbig;
+  float* kbig;
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
 
@@ -270,8 +276,8 @@ KREA_CUDA_API int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args*
  * gate / up columns interleaved in groups of 32 (tools/convert.py); column layout of the fused projection:
  * q [heads*128] | k [kv_heads*128] | v [kv_heads*128] | gate [heads*128] (model.mm:282-288).  The rows are
  * [text ; image] tokens; cos / sin are their [rows, 64] tables.  Seven kernels: two norms, four GEMMs (the
- * first with the fused QK-norm epilogue) and the attention.  Not handled here: int8 weights, the fp32
- * big-dimension split of the reference's block 0, the GPU/ANE hybrid schedule.
+ * first with the fused QK-norm epilogue) and the attention.  Not handled here: int8 weights, the GPU/ANE
+ * hybrid schedule.
  * Workspace: krea_cuda_dit_block_workspace_bytes; pass a buffer or let the handle own one. */
 typedef struct {
   float* x;
@@ -288,6 +294,10 @@ typedef struct {
   float eps;
   void* workspace;
   size_t workspace_bytes;
+  /* the reference's block 0 (model.mm:226-239): use_big_dim != 0 routes head dimension big_dim of q and k
+   * through fp32 side buffers (in the workspace) and the attention's QB / KB term */
+  int use_big_dim;
+  int big_dim;
 } krea_cuda_dit_block_args;
 KREA_CUDA_API size_t krea_cuda_dit_block_workspace_bytes(const krea_cuda_dit_block_args* a);
 KREA_CUDA_API int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a);

@@ -60,7 +60,8 @@ class GemmArgs(ctypes.Structure):
     _fields_ = [("A", _vp), ("W", _vp), ("C", _vp), ("M", _int), ("N", _int), ("K", _int),
                 ("lda", _int), ("ldw", _int), ("ldc", _int), ("epilogue", _int),
                 ("q_off", _int), ("n_q", _int), ("k_off", _int), ("n_k", _int),
-                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int), ("vec", _vp)]
+                ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int), ("vec", _vp),
+                ("big_dim", _int), ("qbig", _vp), ("kbig", _vp)]
 
 
 class RmsNormArgs(ctypes.Structure):
@@ -72,7 +73,7 @@ class DitBlockArgs(ctypes.Structure):
     _fields_ = [("x", _vp), ("mods", _vp), ("w_qkvg", _vp), ("w_o", _vp), ("w_gu", _vp), ("w_down", _vp),
                 ("qn", _vp), ("kn", _vp), ("cos", _vp), ("sin", _vp),
                 ("rows", _int), ("heads", _int), ("kv_heads", _int), ("ff", _int), ("eps", ctypes.c_float),
-                ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t)]
+                ("workspace", _vp), ("workspace_bytes", ctypes.c_size_t), ("use_big_dim", _int), ("big_dim", _int)]
 
 
 class QwInfo(ctypes.Structure):

@@ -141,6 +141,11 @@ struct GemmParams {
   // weights imply (128 * max|wq| * max|wk|, 2 % head-room), for the attention kernel's bounded softmax
   float* bound_out;
   float bound_scale_log2;
+  // epi 1, optional (norm.metal:127-132): head dimension big_dim of every Q / K head goes to qbig [M, n_q] /
+  // kbig [M, n_k] in fp32 and is stored as zero in C; big_dim < 0 = off
+  int big_dim;
+  float* qbig;
+  float* kbig;
   uint32_t* status;
 };
 // A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.

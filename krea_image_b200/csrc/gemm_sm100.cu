@@ -244,10 +244,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int col0 = n0 + hb * 128;
         if (col0 >= p.N) break;
         // which treatment this block of columns gets: 0 plain, 1 Q head, 2 K head
-        int kind = 0;
+        int kind = 0, head = 0;
         if (p.epi == 1) {
-          if (col0 >= p.q_off && col0 < p.q_off + p.n_q * 128) kind = 1;
-          else if (col0 >= p.k_off && col0 < p.k_off + p.n_k * 128) kind = 2;
+          if (col0 >= p.q_off && col0 < p.q_off + p.n_q * 128) { kind = 1; head = (col0 - p.q_off) >> 7; }
+          else if (col0 >= p.k_off && col0 < p.k_off + p.n_k * 128) { kind = 2; head = (col0 - p.k_off) >> 7; }
         }
         float rrms = 1.f;
         if (kind != 0) {
@@ -292,6 +292,18 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                   f[8 * e4 + 2 * q + 1] = x0 * sf[q] + x1 * cf[q];
                 }
               }
+            }
+          }
+          if (kind != 0 && p.big_dim >= 0 && (p.big_dim >> 5) == (c0 >> 5)) {
+            // this head's big dimension: fp32 side buffer, zero in the bf16 row (norm.metal:127-132)
+            const int e = p.big_dim & 31;
+            float v = 0.f;
+#pragma unroll
+            for (int k = 0; k < 32; k++)
+              if (k == e) { v = f[k]; f[k] = 0.f; }
+            if (row < p.M) {
+              if (kind == 1) p.qbig[(size_t)row * p.n_q + head] = v;
+              else p.kbig[(size_t)row * p.n_k + head] = v;
             }
           }
           if (row < p.M) {

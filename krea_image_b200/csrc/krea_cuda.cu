@@ -758,6 +758,11 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
     p.q_off = a->q_off; p.n_q = a->n_q; p.k_off = a->k_off; p.n_k = a->n_k;
     p.wq = a->wq ? a->wq : a->wk; p.wk = a->wk ? a->wk : a->wq;
     p.cos = a->cos; p.sin = a->sin; p.row0 = a->row0; p.eps = a->eps; p.rope_mode = a->rope_mode;
+    p.big_dim = -1;
+    if (a->qbig || a->kbig) {
+      if (!a->qbig || !a->kbig || a->big_dim < 0 || a->big_dim >= 128) return fail(h, KREA_CUDA_E_ARG, "gemm: big_dim needs both side buffers and 0 <= big_dim < 128");
+      p.big_dim = a->big_dim; p.qbig = a->qbig; p.kbig = a->kbig;
+    }
     if (bound_out && a->n_q > 0 && a->n_k > 0) {
       p.bound_out = bound_out;
       p.bound_scale_log2 = (float)(1.0 / sqrt(128.0) * 1.4426950408889634);
@@ -801,7 +806,7 @@ int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args* a) {
 
 // byte offsets of the block's intermediates inside its workspace: h | qkvg | ao | mid
 struct BlockLayout {
-  size_t h, qkvg, ao, mid, total;
+  size_t h, qkvg, ao, mid, qbig, kbig, total;
   int dim, qkvg_cols;
 };
 static BlockLayout block_layout(const krea_cuda_dit_block_args* a) {
@@ -814,7 +819,9 @@ static BlockLayout block_layout(const krea_cuda_dit_block_args* a) {
   l.qkvg = l.h + up(rows * l.dim * 2);
   l.ao = l.qkvg + up(rows * l.qkvg_cols * 2);
   l.mid = l.ao + up(rows * l.dim * 2);
-  l.total = l.mid + up(rows * (size_t)(a->ff > 0 ? a->ff : 0) * 2);
+  l.qbig = l.mid + up(rows * (size_t)(a->ff > 0 ? a->ff : 0) * 2);
+  l.kbig = l.qbig + up(rows * (size_t)a->heads * 4);
+  l.total = l.kbig + up(rows * (size_t)a->kv_heads * 4);
   return l;
 }
 
@@ -865,6 +872,10 @@ int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a) {
   g1.epilogue = KREA_CUDA_EPI_QKNORM_ROPE;
   g1.q_off = 0; g1.n_q = H; g1.k_off = D; g1.n_k = KV;
   g1.wq = a->qn; g1.wk = a->kn; g1.cos = a->cos; g1.sin = a->sin; g1.row0 = 0; g1.eps = a->eps; g1.rope_mode = KREA_CUDA_ROPE_PAIRS;
+  if (a->use_big_dim) {
+    if (a->big_dim < 0 || a->big_dim >= 128) return fail(h, KREA_CUDA_E_ARG, "dit_block: big_dim must be in [0, 128)");
+    g1.big_dim = a->big_dim; g1.qbig = (float*)(ws + l.qbig); g1.kbig = (float*)(ws + l.kbig);
+  }
   float* bound = (float*)(h->status_dev + 8);         // the device float the fused call's pre-pass uses too
   if ((rc = gemm_impl(h, &g1, bound))) return rc;
   // 3. ao = attention(q, k, v) * sigmoid(gate)                                  (model.mm:282-288, 377)
@@ -877,6 +888,7 @@ int krea_cuda_dit_block(krea_cuda* h, const krea_cuda_dit_block_args* a) {
   at.ldq = QC; at.ldk = QC; at.ldv = QC; at.ldo = D; at.ldg = QC;
   at.logit_bound = bound;
   at.bound_given = true;
+  if (a->use_big_dim) { at.QB = (const float*)(ws + l.qbig); at.KB = (const float*)(ws + l.kbig); }
   if ((rc = run_attention(h, at))) return rc;
   // 4. x += gate1 * (ao Wo)                                                     (model.mm:357-359, 379)
   krea_cuda_gemm_args g2 = {};

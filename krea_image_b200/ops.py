@@ -151,6 +151,7 @@ class KreaCuda:
             a.wq, a.wk = _ptr(qk_norm.get("wq")), _ptr(qk_norm.get("wk"))
             a.cos, a.sin = _ptr(qk_norm.get("cos")), _ptr(qk_norm.get("sin"))
             a.row0, a.eps, a.rope_mode = qk_norm.get("row0", 0), qk_norm.get("eps", 1e-6), qk_norm.get("rope_mode", B.ROPE_PAIRS)
+            a.big_dim, a.qbig, a.kbig = qk_norm.get("big_dim", 0), _ptr(qk_norm.get("qbig")), _ptr(qk_norm.get("kbig"))
         self._check(self.lib.krea_cuda_gemm(self.h, ctypes.byref(a)))
 
     def rms_norm(self, x, mul, add, y, rows, width, ld_in, ld_out, eps, f32_out=False):
@@ -158,11 +159,13 @@ class KreaCuda:
         a = B.RmsNormArgs(_ptr(x), _ptr(mul), _ptr(add), _ptr(y), rows, width, ld_in, ld_out, eps, int(bool(f32_out)))
         self._check(self.lib.krea_cuda_rms_norm(self.h, ctypes.byref(a)))
 
-    def dit_block(self, x, mods, w_qkvg, w_o, w_gu, w_down, qn, kn, cos, sin, rows, heads, kv_heads, ff, eps=1e-6, workspace=None):
+    def dit_block(self, x, mods, w_qkvg, w_o, w_gu, w_down, qn, kn, cos, sin, rows, heads, kv_heads, ff, eps=1e-6, workspace=None,
+                  big_dim=-1):
         """DiT::layer (engine/src/model.mm:369-385) on the fp32 residual stream x [rows, heads*128], in place."""
         a = B.DitBlockArgs(_ptr(x), _ptr(mods), _ptr(w_qkvg), _ptr(w_o), _ptr(w_gu), _ptr(w_down), _ptr(qn), _ptr(kn),
                            _ptr(cos), _ptr(sin), rows, heads, kv_heads, ff, eps, _ptr(workspace),
-                           0 if workspace is None else workspace.numel() * workspace.element_size())
+                           0 if workspace is None else workspace.numel() * workspace.element_size(),
+                           int(big_dim >= 0), max(big_dim, 0))
         self._check(self.lib.krea_cuda_dit_block(self.h, ctypes.byref(a)))
 
     def layerwise_attn(self, qkvg, out, rows, ld, ldo, heads, q_off, k_off, v_off, g_off):

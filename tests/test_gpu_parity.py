@@ -167,6 +167,37 @@ def test_attention_causal(kc, Lq, Lk, q_pos0, H, group):
         assert np.all(got[:-q_pos0] == 0)
 
 
+def test_text_encoder_style_call_with_prefix_keys(kc):
+    """The Qwen3 encoder's call sequence (engine/src/model.mm:141-157): new rows [L0, L) of a fused q|k|v buffer are
+    normalised and rotated in place (rotate-half RoPE, tables offset by L0, GQA 4:1), the first L0 key / value rows
+    come from a prefix cache, and the new rows attend causally over all L keys with q_pos0 = L0."""
+    rng = np.random.default_rng(88)
+    Hq, Hkv, L0, L = 8, 2, 70, 70 + 150
+    ld = (Hq + 2 * Hkv) * 128
+    Lr = L - L0
+    buf = synth.f32_to_bf16_bits(rng.standard_normal((L, ld)).astype(np.float32))     # rows [0, L0): cached, already normalised k | v
+    wq = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    wk = rng.uniform(0.5, 1.5, 128).astype(np.float32)
+    pos = np.arange(L, dtype=np.float64)[:, None] / np.power(1e6, np.arange(64, dtype=np.float64) / 64.0)[None, :]
+    cos, sin = np.cos(pos).astype(np.float32), np.sin(pos).astype(np.float32)
+    want_buf = buf.copy()
+    new_rows = want_buf[L0:]                                                           # a view: the oracle works in place
+    oracle.qk_norm_rope(new_rows, wq, wk, cos[L0:], sin[L0:], Lr, ld, 0, Hq, Hq * 128, Hkv, 1e-6, 1)
+    flat = want_buf.reshape(-1)
+    want = oracle.attention(flat[L0 * ld:], flat[Hq * 128:], flat[(Hq + Hkv) * 128:], Lr, L, Hq, ld, ld, ld, group=Hq // Hkv,
+                            causal=True, q_pos0=L0)
+    x = dev_bits(buf)
+    xf = x.view(-1)
+    d_cos, d_sin = dev_f32(cos), dev_f32(sin)
+    kc.qk_norm_rope(xf[L0 * ld:], dev_f32(wq), dev_f32(wk), d_cos.view(-1)[L0 * 64:], d_sin.view(-1)[L0 * 64:], Lr, ld, 0, Hq, Hq * 128, Hkv,
+                    1e-6, 1)
+    o = torch.zeros((Lr, Hq * 128), dtype=torch.bfloat16, device="cuda")
+    kc.attention(xf[L0 * ld:], xf[Hq * 128:], xf[(Hq + Hkv) * 128:], o, Lr, L, Hq, ld, ld, ld, Hq * 128, Hq // Hkv, True, L0)
+    kc.wait()
+    check(host_f32(o), want, None, "encoder-style call")
+    assert np.array_equal(x.view(torch.int16).cpu().numpy().view(np.uint16)[:L0], buf[:L0])      # the prefix rows are untouched
+
+
 def test_attention_big_dim_rank1_term(kc):
     """Block 0 of the reference model: one head dimension is split off in fp32 by qk_norm_rope (big_dim) and
     comes back as the rank-1 score term QB[q, h] * KB[k, h / group] (norm.metal:68-71, attention.metal:232-234)."""

@@ -220,8 +220,8 @@ KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwi
  * the projection writes Q and K already normalised and rotated (rope_mode 0 or 2; cos/sin row = row0 + output
  * row); the attention is then called through krea_cuda_attention on the result.
  * KREA_CUDA_EPI_RESID_GATE / _SWIGLU are the epilogues of the O-projection and of the MLP (model.mm:357-366).
- * Not built: int8 weights with group scales (Weight::q8), the F32 / GELU / bias epilogues, the LoRA term, the
- * column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * int8 weights (Weight::q8) are dequantised once with krea_cuda_dequant_q8 and then used as bf16.  Not built: the
+ * F32 / GELU / bias epilogues, the LoRA term, the column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
  * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
 #define KREA_CUDA_EPI_BF16 0
 #define KREA_CUDA_EPI_QKNORM_ROPE 1
@@ -251,6 +251,20 @@ typedef struct {
   float* kbig;
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
+
+/* ---- int8 weights (the reference's Weight::q8, engine/src/metal.h:25-29) ----
+ * Wq int8 [K, N] with f32 scales [K / 128, N] (tools/convert.py:92-99) -> bf16 [K, N], every value
+ * bf16(float(q) * s) exactly as the reference's GEMM dequantises it on the fly (gemm.metal:159-170).  Done once
+ * per matrix at load time; krea_cuda_gemm then runs on the bf16 copy.  K a multiple of 128 (metal.mm:151), N of
+ * 16; leading dimensions in elements; pointers 16-byte aligned. */
+typedef struct {
+  const void* wq;
+  const float* scales;
+  void* out;
+  int K, N;
+  int ldq, lds, ldo;
+} krea_cuda_dequant_args;
+KREA_CUDA_API int krea_cuda_dequant_q8(krea_cuda* h, const krea_cuda_dequant_args* a);
 
 /* ---- Metal::rms_norm (engine/src/metal.h:75-77; kernel norm.metal:28-55) ----
  * y[row, c] = x[row, c] * rsqrt(mean_c(x[row]^2) + eps) * mul[c] (+ add[c]); x f32 [rows, ld_in], y bf16 (or f32

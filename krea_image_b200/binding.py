@@ -64,6 +64,10 @@ class GemmArgs(ctypes.Structure):
                 ("big_dim", _int), ("qbig", _vp), ("kbig", _vp)]
 
 
+class DequantArgs(ctypes.Structure):
+    _fields_ = [("wq", _vp), ("scales", _vp), ("out", _vp), ("K", _int), ("N", _int), ("ldq", _int), ("lds", _int), ("ldo", _int)]
+
+
 class RmsNormArgs(ctypes.Structure):
     _fields_ = [("x", _vp), ("mul", _vp), ("add", _vp), ("y", _vp), ("rows", _int), ("width", _int), ("ld_in", _int),
                 ("ld_out", _int), ("eps", ctypes.c_float), ("f32_out", _int)]
@@ -112,6 +116,7 @@ SYMBOLS = {
     "krea_cuda_rope_tables_ref3axis": (_int, [_vp, _vp, _int, _int, _int]),
     "krea_cuda_rope_tables_axial2d": (_int, [_vp, _vp, _int, _int, _int, ctypes.c_double]),
     "krea_cuda_gemm": (_int, [_vp, ctypes.POINTER(GemmArgs)]),
+    "krea_cuda_dequant_q8": (_int, [_vp, ctypes.POINTER(DequantArgs)]),
     "krea_cuda_rms_norm": (_int, [_vp, ctypes.POINTER(RmsNormArgs)]),
     "krea_cuda_dit_block_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(DitBlockArgs)]),
     "krea_cuda_dit_block": (_int, [_vp, ctypes.POINTER(DitBlockArgs)]),

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT_DIR, "libkrea_cuda.so")
-SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "qk_norm_rope.cu", "layerwise_attn.cu", "gemm_sm100.cu", "rms_norm.cu", "dist_nccl.cu", "qw_file.cu"]
+SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "qk_norm_rope.cu", "layerwise_attn.cu", "gemm_sm100.cu", "rms_norm.cu", "dequant_q8.cu", "dist_nccl.cu", "qw_file.cu"]
 HEADERS = ["attention_sm100.h", "sm100_ptx.cuh", "handle.h", os.path.join("..", "..", "include", "krea_cuda.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]

@@ -785,6 +785,22 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
 
 int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a) { return gemm_impl(h, a, nullptr); }
 
+int krea_cuda_dequant_q8(krea_cuda* h, const krea_cuda_dequant_args* a) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "dequant_q8: null handle or arguments");
+  if (a->K < 0 || a->N < 0) return fail(h, KREA_CUDA_E_ARG, "dequant_q8: negative size");
+  if (a->K == 0 || a->N == 0) return KREA_CUDA_OK;
+  if (a->K % 128 || a->N % 16) return fail(h, KREA_CUDA_E_ARG, "dequant_q8: K must be a multiple of 128 (the scale group) and N of 16");
+  if (!a->wq || !a->scales || !a->out || !aligned16(a->wq) || !aligned16(a->scales) || !aligned16(a->out)) return fail(h, KREA_CUDA_E_ARG, "dequant_q8: null or misaligned pointer");
+  if (a->ldq % 16 || a->lds % 4 || a->ldo % 8 || a->ldq < a->N || a->lds < a->N || a->ldo < a->N) return fail(h, KREA_CUDA_E_ARG, "dequant_q8: bad leading dimension");
+  DequantParams p{};
+  p.wq = (const int8_t*)a->wq; p.scales = a->scales; p.out = (__nv_bfloat16*)a->out;
+  p.K = a->K; p.N = a->N; p.ldq = a->ldq; p.lds = a->lds; p.ldo = a->ldo;
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, launch_dequant_q8(p, h->stream));
+  h->launches++;
+  return KREA_CUDA_OK;
+}
+
 int krea_cuda_rms_norm(krea_cuda* h, const krea_cuda_rmsnorm_args* a) {
   if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "rms_norm: null handle or arguments");
   if (a->rows < 0 || a->width < 0) return fail(h, KREA_CUDA_E_ARG, "rms_norm: negative size");

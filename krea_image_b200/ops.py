@@ -154,6 +154,11 @@ class KreaCuda:
             a.big_dim, a.qbig, a.kbig = qk_norm.get("big_dim", 0), _ptr(qk_norm.get("qbig")), _ptr(qk_norm.get("kbig"))
         self._check(self.lib.krea_cuda_gemm(self.h, ctypes.byref(a)))
 
+    def dequant_q8(self, wq, scales, out, K, N, ldq=None, lds=None, ldo=None):
+        """int8 [K, N] + f32 scales [K/128, N] -> bf16 [K, N], bf16(float(q) * s) (gemm.metal:159-170)."""
+        a = B.DequantArgs(_ptr(wq), _ptr(scales), _ptr(out), K, N, N if ldq is None else ldq, N if lds is None else lds, N if ldo is None else ldo)
+        self._check(self.lib.krea_cuda_dequant_q8(self.h, ctypes.byref(a)))
+
     def rms_norm(self, x, mul, add, y, rows, width, ld_in, ld_out, eps, f32_out=False):
         """Metal::rms_norm (engine/src/metal.h:75-77): same argument order."""
         a = B.RmsNormArgs(_ptr(x), _ptr(mul), _ptr(add), _ptr(y), rows, width, ld_in, ld_out, eps, int(bool(f32_out)))

@@ -120,13 +120,24 @@ class BlockWeights:
         self.segment = torch.empty(length, dtype=torch.uint8, device=f"cuda:{kc.device}")
         wf.upload(kc, off, length, self.segment)
         self.info = {}
+        tdt = {"bf16": torch.bfloat16, "f32": torch.float32, "i8": torch.int8, "f16": torch.float16}
+
+        def view(name):
+            ti = wf.info(name)
+            raw = self.segment[ti.offset - off:ti.offset - off + ti.nbytes]
+            return ti, raw.view(tdt[ti.dtype]).view(ti.shape)
         for n in self.NAMES:
-            ti = wf.info(prefix + n)
-            view = self.segment[ti.offset - off:ti.offset - off + ti.nbytes]
+            ti, t = view(prefix + n)
             self.info[n] = ti
-            setattr(self, n, view.view(torch.bfloat16 if ti.dtype == "bf16" else torch.float32).view(ti.shape))
-        if self.qkvg.dtype != torch.bfloat16:
-            raise ValueError("only bf16 weights are supported (the file holds int8 weights with group scales)")
+            if ti.dtype == "i8":
+                # Weight::q8 (weights.h:36-39: companion `<name>.s`): dequantised once into a bf16 copy - the values the
+                # reference's GEMM forms tile by tile - because 180 GB of HBM have room for it
+                _, sc = view(prefix + n + ".s")
+                K, N = ti.shape
+                full = torch.empty((K, N), dtype=torch.bfloat16, device=t.device)
+                kc.dequant_q8(t, sc, full, K, N)
+                t = full
+            setattr(self, n, t)
 
     def run(self, kc, x, mods, cos, sin, rows, heads, kv_heads, eps=1e-6):
         """DiT::layer on the residual stream x with this layer's weights."""

@@ -36,7 +36,7 @@ def test_struct_layouts_match_header_field_order():
     text = open(os.path.join(ROOT, "include", "krea_cuda.h")).read()
     for cname, st in (("krea_cuda_qknorm_args", binding.QKNormArgs), ("krea_cuda_attn_args", binding.AttnArgs),
                       ("krea_cuda_joint_args", binding.JointArgs), ("krea_cuda_reshard_args", binding.ReshardArgs),
-                      ("krea_cuda_layerwise_args", binding.LayerwiseArgs), ("krea_cuda_gemm_args", binding.GemmArgs), ("krea_cuda_rmsnorm_args", binding.RmsNormArgs),
+                      ("krea_cuda_layerwise_args", binding.LayerwiseArgs), ("krea_cuda_gemm_args", binding.GemmArgs), ("krea_cuda_rmsnorm_args", binding.RmsNormArgs), ("krea_cuda_dequant_args", binding.DequantArgs),
                       ("krea_cuda_dit_block_args", binding.DitBlockArgs), ("krea_cuda_a2a_args", binding.A2AArgs), ("krea_cuda_seqpar_args", binding.SeqParArgs)):
         end = text.index("} " + cname + ";")
         body = text[text.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
@@ -73,6 +73,7 @@ def test_host_side_argument_errors():
     assert lib.krea_cuda_layerwise_attn(None, None) == binding.E_ARG
     assert lib.krea_cuda_gemm(None, None) == binding.E_ARG
     assert lib.krea_cuda_rms_norm(None, None) == binding.E_ARG
+    assert lib.krea_cuda_dequant_q8(None, None) == binding.E_ARG
     assert lib.krea_cuda_dit_block(None, None) == binding.E_ARG
     assert lib.krea_cuda_dit_block_workspace_bytes(None) == 0
     # the sequence-parallel entry points need a handle with a communicator

@@ -162,6 +162,38 @@ def test_gemm_tile_width_variants(monkeypatch):
     assert rel <= 3e-3
 
 
+def _q8(w):
+    """tools/convert.py:92-99: symmetric int8 per output column and group of 128 input rows."""
+    K, N = w.shape
+    g = w.reshape(K // 128, 128, N)
+    scale = np.maximum(np.abs(g).max(axis=1), 1e-12) / 127.0
+    q = np.clip(np.rint(g / scale[:, None, :]), -127, 127).reshape(K, N)
+    return q.astype(np.int8), scale.astype(np.float32)
+
+
+def test_dequant_q8_bit_exact_and_feeds_the_gemm(kc):
+    """Weight::q8 (gemm.metal:159-170): d = bf16(float(q) * s).  Integer and byte work: bit-exact against numpy."""
+    rng = np.random.default_rng(51)
+    K, N, M = 384, 272, 200
+    q, sc = _q8((rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32))
+    want_bits = synth.f32_to_bf16_bits(q.astype(np.float32) * np.repeat(sc, 128, axis=0)).reshape(K, N)
+    out = torch.zeros((K, N + 8), dtype=torch.bfloat16, device="cuda")
+    kc.dequant_q8(torch.from_numpy(q).cuda(), torch.from_numpy(sc).cuda(), out, K, N, N, N, N + 8)
+    kc.wait()
+    got_bits = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got_bits[:, :N], want_bits) and not got_bits[:, N:].any()
+    # ... and the product with the dequantised copy equals the product the reference forms tile by tile
+    a = _bits(rng.standard_normal((M, K)))
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), out, c, M, N, K, K, N + 8, N)
+    kc.wait()
+    want = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(want_bits).astype(np.float64)
+    rel, _ = _rel(c.float().cpu().numpy(), want)
+    assert rel <= 3e-3
+    with pytest.raises(ops.KreaCudaError):
+        kc.dequant_q8(torch.from_numpy(q).cuda(), torch.from_numpy(sc).cuda(), out, K - 64, N, N, N, N + 8)    # not whole scale groups
+
+
 def test_gemm_model_size_projection(kc):
     """The q|k|v projection at the headline configuration's size (4608 x 9216 x 3072) against float32 numpy."""
     M, N, K = 4608, 9216, 3072

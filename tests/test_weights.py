@@ -184,5 +184,34 @@ def test_block_weights_from_file_drive_the_dit_block(tmp_path):
                          S, heads, kv, ff)
             kc.wait()
             assert torch.equal(x, x2) and bool(torch.isfinite(x).all()) and not torch.equal(x, dev(x0))
+        # the same layer stored as int8 + group scales (the converter's `dit_q8.qw` flavour): dequantised at load
+        # time into the values the reference's GEMM would form, then the same block call
+        def q8(wb):
+            w = synth.bf16_bits_to_f32(wb)
+            K, N = w.shape
+            g = w.reshape(K // 128, 128, N)
+            scale = np.maximum(np.abs(g).max(axis=1), 1e-12) / 127.0
+            return np.clip(np.rint(g / scale[:, None, :]), -127, 127).reshape(K, N).astype(np.int8), scale.astype(np.float32)
+        ts8 = []
+        for n, dt, a in ts:
+            if n.startswith("L1.") and dt == "bf16":
+                q, sc = q8(a)
+                ts8 += [(n, "i8", q), (n + ".s", "f32", sc)]
+            elif n.startswith("L1."):
+                ts8.append((n, dt, a))
+        path8 = tmp_path / "dit_q8.qw"
+        write_qw(path8, ts8, meta={"q8": True})
+        with weights.WeightFile(path8) as w8:
+            bw8 = weights.BlockWeights(kc, w8, 1)
+            kc.wait()
+            deq = bw8.qkvg.float().cpu().numpy()
+            q, sc = q8(t["L1.qkvg"])
+            want = synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(q.astype(np.float32) * np.repeat(sc, 128, axis=0))).reshape(q.shape)
+            assert np.array_equal(deq, want)
+            x8 = dev(x0)
+            bw8.run(kc, x8, dev(mods), dev(cos), dev(sin), S, heads, kv)
+            kc.wait()
+            upd, upd8 = (x - dev(x0)).double(), (x8 - dev(x0)).double()
+            assert float((upd - upd8).norm() / upd.norm()) < 5e-2       # int8 weights: a percent-level change of the update
     finally:
         kc.close()

@@ -221,12 +221,16 @@ KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwi
  * row); the attention is then called through krea_cuda_attention on the result.
  * KREA_CUDA_EPI_RESID_GATE / _SWIGLU are the epilogues of the O-projection and of the MLP (model.mm:357-366).
  * int8 weights (Weight::q8) are dequantised once with krea_cuda_dequant_q8 and then used as bf16.  Not built: the
- * F32 / GELU / bias epilogues, the LoRA term, the column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * LoRA term and the column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
  * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
 #define KREA_CUDA_EPI_BF16 0
 #define KREA_CUDA_EPI_QKNORM_ROPE 1
 #define KREA_CUDA_EPI_RESID_GATE 2 /* C is f32 [M, N]: C += vec[n] * acc (gemm.metal:262-264); vec NULL: C += acc (Epi::Resid) */
 #define KREA_CUDA_EPI_SWIGLU 3     /* C is bf16 [M, N/2]: silu(gate) * up on tile-interleaved weights (gemm.metal:233-250); N % 64 == 0 */
+#define KREA_CUDA_EPI_F32 4        /* C is f32: C = acc (Epi::F32) */
+#define KREA_CUDA_EPI_GELU 5       /* C is bf16: gelu_tanh(acc) (Epi::GELU, common.h:26-29) */
+#define KREA_CUDA_EPI_BIAS_BF16 6  /* C is bf16: acc + vec[n] (Epi::BiasBF16) */
+#define KREA_CUDA_EPI_BIAS_F32 7   /* C is f32: acc + vec[n] (Epi::BiasF32) */
 typedef struct {
   const void* A;
   const void* W;
@@ -242,7 +246,7 @@ typedef struct {
   int row0;
   float eps;
   int rope_mode;
-  const float* vec;   /* RESID_GATE: per-column gate, f32 [N] (the reference's `vec` argument) */
+  const float* vec;   /* RESID_GATE: per-column gate; BIAS_*: per-column bias; f32 [N] (the reference's `vec` argument) */
   /* QKNORM_ROPE, optional (qk_norm_rope's big_dim, norm.metal:127-132): when qbig and kbig are given, head
    * dimension big_dim of every Q / K head is written to qbig [M, n_q] / kbig [M, n_k] in fp32 and stored as
    * zero in C, for the attention's QB / KB term.  NULL = off (big_dim ignored). */

@@ -11,7 +11,7 @@ from . import build as _build
 
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM, E_COMM, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
-EPI_BF16, EPI_QKNORM_ROPE, EPI_RESID_GATE, EPI_SWIGLU = 0, 1, 2, 3
+EPI_BF16, EPI_QKNORM_ROPE, EPI_RESID_GATE, EPI_SWIGLU, EPI_F32, EPI_GELU, EPI_BIAS_BF16, EPI_BIAS_F32 = 0, 1, 2, 3, 4, 5, 6, 7
 STATIC_SCRATCH_BYTES = 32 << 20   # KREA_CUDA_STATIC_SCRATCH_BYTES
 DIST_ID_BYTES = 128                # KREA_CUDA_DIST_ID_BYTES
 

@@ -137,8 +137,9 @@ struct GemmParams {
   int64_t ldc;
   int M, N, K;
   int epi;                      // 0: bf16 store; 1: Q / K head blocks are RMS-normalised, weighted and rotated first;
-                                // 2: C is fp32 and receives += vec[col] * acc (vec nullptr: += acc); 3: SwiGLU, C has N / 2 columns
-  const float* vec;             // epi 2: per-column gate
+                                // 2: C is fp32 and receives += vec[col] * acc (vec nullptr: += acc); 3: SwiGLU, C has N / 2 columns;
+                                // 4: fp32 store; 5: gelu_tanh, bf16; 6: + vec[col], bf16; 7: + vec[col], fp32
+  const float* vec;             // epi 2: per-column gate; epi 6, 7: per-column bias
   int q_off, n_q, k_off, n_k;   // epi 1: output columns of the Q and K heads (multiples of 128) and head counts
   const float* wq;
   const float* wk;

@@ -238,6 +238,44 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
+      } else if (p.epi >= 4) {
+        // Epi::F32 (4), Epi::GELU (5), Epi::BiasBF16 (6), Epi::BiasF32 (7): gemm.metal:257-260, 268-277
+        const bool f32_out = p.epi == 4 || p.epi == 7;
+        float* xrow = (float*)p.C + (size_t)min(row, p.M - 1) * p.ldc;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          const int col0 = n0 + c0;
+          if (col0 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld32(lane_addr + a * BN + c0, v);
+          tmem_wait_ld();
+          if (row < p.M) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int col = col0 + q4 * 8;
+              if (col + 8 > p.N) continue;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; e++) f[e] = __uint_as_float(v[q4 * 8 + e]);
+              if (p.epi >= 6) {
+                const float4 b0 = __ldg((const float4*)(p.vec + col)), b1 = __ldg((const float4*)(p.vec + col) + 1);
+                f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w; f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+              } else if (p.epi == 5) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) {          // common.h:26-29 gelu_tanh
+                  const float x = f[e];
+                  f[e] = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+                }
+              }
+              if (f32_out) {
+                *(float4*)(xrow + col) = make_float4(f[0], f[1], f[2], f[3]);
+                *(float4*)(xrow + col + 4) = make_float4(f[4], f[5], f[6], f[7]);
+              } else {
+                *(uint4*)(crow + col) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+              }
+            }
+          }
+        }
       } else
 #pragma unroll 1
       for (int hb = 0; hb < BN / 128; hb++) {             // one block of 128 columns (one head) at a time

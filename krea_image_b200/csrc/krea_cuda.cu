@@ -734,7 +734,9 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
   if (a->K == 0) return fail(h, KREA_CUDA_E_ARG, "gemm: K must be positive");
   if (!a->A || !a->W || !a->C || !aligned16(a->A) || !aligned16(a->W) || !aligned16(a->C)) return fail(h, KREA_CUDA_E_ARG, "gemm: null or misaligned pointer");
   if (a->lda % 8 || a->ldw % 8 || a->ldc % 8 || a->N % 8 || a->K % 8) return fail(h, KREA_CUDA_E_ARG, "gemm: lda, ldw, ldc, N and K must be multiples of 8");
-  if (a->epilogue < KREA_CUDA_EPI_BF16 || a->epilogue > KREA_CUDA_EPI_SWIGLU) return fail(h, KREA_CUDA_E_UNSUPPORTED, "gemm: epilogue %d is not built", a->epilogue);
+  if (a->epilogue < KREA_CUDA_EPI_BF16 || a->epilogue > KREA_CUDA_EPI_BIAS_F32) return fail(h, KREA_CUDA_E_UNSUPPORTED, "gemm: epilogue %d is not built", a->epilogue);
+  const bool has_bias = a->epilogue == KREA_CUDA_EPI_BIAS_BF16 || a->epilogue == KREA_CUDA_EPI_BIAS_F32;
+  if (has_bias && (!a->vec || !aligned16(a->vec))) return fail(h, KREA_CUDA_E_ARG, "gemm: the bias vector is missing or misaligned");
   const int out_cols = a->epilogue == KREA_CUDA_EPI_SWIGLU ? a->N / 2 : a->N;
   if (a->lda < a->K || a->ldw < a->N || a->ldc < out_cols) return fail(h, KREA_CUDA_E_ARG, "gemm: a leading dimension is smaller than its row");
   if (a->epilogue == KREA_CUDA_EPI_SWIGLU && a->N % 64) return fail(h, KREA_CUDA_E_ARG, "gemm: SwiGLU needs N to be a multiple of 64 (32 gate + 32 up columns per group)");
@@ -745,7 +747,7 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.status = h->status_dev;
   p.epi = a->epilogue;
-  p.vec = a->epilogue == KREA_CUDA_EPI_RESID_GATE ? a->vec : nullptr;
+  p.vec = (a->epilogue == KREA_CUDA_EPI_RESID_GATE || has_bias) ? a->vec : nullptr;
   if (a->epilogue == KREA_CUDA_EPI_QKNORM_ROPE) {
     if (a->rope_mode == KREA_CUDA_ROPE_HALF) return fail(h, KREA_CUDA_E_UNSUPPORTED, "gemm: the fused epilogue rotates interleaved pairs only (rope_mode 0 or 2)");
     if (a->rope_mode != KREA_CUDA_ROPE_PAIRS && a->rope_mode != KREA_CUDA_ROPE_NONE) return fail(h, KREA_CUDA_E_ARG, "gemm: bad rope_mode");

@@ -162,6 +162,33 @@ def test_gemm_tile_width_variants(monkeypatch):
     assert rel <= 3e-3
 
 
+@pytest.mark.parametrize("epi", ["f32", "gelu", "bias_bf16", "bias_f32"])
+def test_gemm_remaining_epilogues(kc, epi):
+    """Epi::F32, Epi::GELU, Epi::BiasBF16, Epi::BiasF32 (gemm.metal:257-260, 268-277)."""
+    M, N, K = 150, 264, 136
+    a, w = _case(61, M, N, K, K, N)
+    rng = np.random.default_rng(62)
+    bias = rng.standard_normal(N).astype(np.float32)
+    acc = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+    code = {"f32": binding.EPI_F32, "gelu": binding.EPI_GELU, "bias_bf16": binding.EPI_BIAS_BF16, "bias_f32": binding.EPI_BIAS_F32}[epi]
+    f32_out = epi in ("f32", "bias_f32")
+    want = {"f32": acc, "gelu": 0.5 * acc * (1.0 + np.tanh(0.7978845608028654 * (acc + 0.044715 * acc ** 3))),
+            "bias_bf16": acc + bias, "bias_f32": acc + bias}[epi]
+    c = torch.full((M, N + 8), float("nan"), dtype=torch.float32 if f32_out else torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N + 8, epilogue=code, vec=torch.from_numpy(bias).cuda() if "bias" in epi else None)
+    kc.wait()
+    got = c.float().cpu().numpy()
+    if f32_out:
+        assert np.allclose(got[:, :N], want, rtol=1e-4, atol=1e-4)
+    else:
+        rel, mx = _rel(got[:, :N], want)
+        assert rel <= 3e-3, f"rel-L2 {rel:.3e} max-abs {mx:.3e}"
+    assert np.all(np.isnan(got[:, N:]))
+    if "bias" in epi:
+        with pytest.raises(ops.KreaCudaError):
+            kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N + 8, epilogue=code)          # bias vector missing
+
+
 def _q8(w):
     """tools/convert.py:92-99: symmetric int8 per output column and group of 128 input rows."""
     K, N = w.shape

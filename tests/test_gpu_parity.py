@@ -167,6 +167,33 @@ def test_attention_causal(kc, Lq, Lk, q_pos0, H, group):
         assert np.all(got[:-q_pos0] == 0)
 
 
+def test_attention_operator_random_sweep(kc):
+    """Twenty seeded random combinations of sizes and flags (Lq != Lk, ragged tails, GQA, gate, causal with an
+    offset, strides wider than the rows) against the oracle; the output buffer is NaN-filled around the rows and
+    columns the operator owns and must come back untouched there."""
+    rng = np.random.default_rng(2024)
+    for case in range(20):
+        kvh, group = int(rng.integers(1, 4)), int(rng.choice([1, 2, 4]))
+        H = kvh * group
+        Lq, Lk = int(rng.integers(1, 700)), int(rng.integers(1, 900))
+        causal = bool(rng.integers(0, 2))
+        q_pos0 = int(rng.integers(0, max(Lk - Lq, 0) + 40)) if causal else 0
+        gate = bool(rng.integers(0, 2))
+        ldq, ldk, ldv, ldo, ldg = H * 128 + 8 * int(rng.integers(0, 3)), kvh * 128 + 8 * int(rng.integers(0, 3)), kvh * 128, H * 128 + 16, H * 128
+        mk = lambda r, c: synth.f32_to_bf16_bits(rng.standard_normal((r, c)).astype(np.float32)).reshape(r, c)
+        Q, K, V, G = mk(Lq, ldq), mk(Lk, ldk), mk(Lk, ldv), mk(Lq, ldg)
+        want = oracle.attention(Q.reshape(-1), K.reshape(-1), V.reshape(-1), Lq, Lk, H, ldq, ldk, ldv, group=group, causal=causal, q_pos0=q_pos0,
+                                G=G.reshape(-1) if gate else None, ldg=ldg if gate else 0)
+        o = torch.full((Lq + 1, ldo), float("nan"), dtype=torch.bfloat16, device="cuda")
+        kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, ldq, ldk, ldv, ldo, group, causal, q_pos0,
+                     dev_bits(G) if gate else None, ldg if gate else 0)
+        kc.wait()
+        got = host_f32(o)
+        what = f"case {case}: Lq {Lq} Lk {Lk} H {H} group {group} causal {causal} q_pos0 {q_pos0} gate {gate}"
+        check(got[:Lq, :H * 128], want, None, what)
+        assert np.all(np.isnan(got[Lq:])) and np.all(np.isnan(got[:, H * 128:])), what
+
+
 def test_text_encoder_style_call_with_prefix_keys(kc):
     """The Qwen3 encoder's call sequence (engine/src/model.mm:141-157): new rows [L0, L) of a fused q|k|v buffer are
     normalised and rotated in place (rotate-half RoPE, tables offset by L0, GQA 4:1), the first L0 key / value rows

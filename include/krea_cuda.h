@@ -73,6 +73,10 @@ KREA_CUDA_API uint64_t krea_cuda_launch_count(krea_cuda* h);
  * last krea_cuda_profile_enable(h, 1), then clears them. */
 KREA_CUDA_API int krea_cuda_profile_enable(krea_cuda* h, int on);
 KREA_CUDA_API int krea_cuda_profile_read(krea_cuda* h, int which, double* total_ms, int* launches);
+/* The reference's KREA_TRACE=path (engine/src/metal.mm:284-294): writes the marks recorded since the last
+ * krea_cuda_profile_enable(h, 1) - not yet consumed by krea_cuda_profile_read - as Chrome-trace JSON (one
+ * complete event per bracketed launch, microseconds since the enable call), for chrome://tracing / Perfetto. */
+KREA_CUDA_API int krea_cuda_profile_trace(krea_cuda* h, const char* path);
 
 /* ---- Metal::qk_norm_rope (engine/src/metal.h:80-82; kernel engine/kernels/norm.metal:81-134) ----
  * In place on bf16 rows [rows, ld]: for every row and head, x <- bf16(rope(x * rsqrt(mean(x^2) + eps) * w)).

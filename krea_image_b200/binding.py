@@ -107,6 +107,7 @@ SYMBOLS = {
     "krea_cuda_launch_count": (ctypes.c_uint64, [_vp]),
     "krea_cuda_profile_enable": (_int, [_vp, _int]),
     "krea_cuda_profile_read": (_int, [_vp, _int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_int)]),
+    "krea_cuda_profile_trace": (_int, [_vp, ctypes.c_char_p]),
     "krea_cuda_qk_norm_rope": (_int, [_vp, ctypes.POINTER(QKNormArgs)]),
     "krea_cuda_attention": (_int, [_vp, ctypes.POINTER(AttnArgs)]),
     "krea_cuda_joint_scratch_bytes": (ctypes.c_size_t, [ctypes.POINTER(JointArgs)]),

@@ -188,9 +188,10 @@ static int heads_to_seq_on(krea_cuda* h, const void* src, void* dst, void* stage
 // ---- peer-store mode ---------------------------------------------------------------------------------
 constexpr size_t XCHG_BYTES = 8 * sizeof(cudaIpcMemHandle_t) + 256;
 
-// All ranks reach this point of their streams: a one-float all-reduce.  Stream-ordered; kernels enqueued
-// after it on any rank start only after every rank's earlier kernels (and their peer stores) have completed.
-static int rank_barrier(krea_cuda* h, cudaStream_t stream, ncclRedOp_t op = ncclSum) {
+// All ranks reach this point of their streams: a one-float all-reduce (max, so the word stays bounded however
+// many barriers pass).  Stream-ordered; kernels enqueued after it on any rank start only after every rank's
+// earlier kernels (and their peer stores) have completed.
+static int rank_barrier(krea_cuda* h, cudaStream_t stream, ncclRedOp_t op = ncclMax) {
   KreaDist* d = h->dist;
   float* w = (float*)(d->xchg + 8 * sizeof(cudaIpcMemHandle_t));
   NCCL_TRY(h, d, d->api->AllReduce(w, w, 1, ncclFloat, op, d->comm, stream));
@@ -221,9 +222,29 @@ static int sym_alloc(krea_cuda* h, size_t bytes) {
   if (d->sym) cudaFree(d->sym);
   d->sym = nullptr;
   d->sym_bytes = 0;
+  float* w = (float*)(d->xchg + 8 * sizeof(cudaIpcMemHandle_t));
+  // the ranks agree on the outcome of a step (minimum of their flags) before any of them moves on: a rank
+  // that failed alone would otherwise leave the others waiting in the next collective
+  auto agree = [&](float mine_ok, float* all_ok) -> int {
+    CUDA_TRY(h, cudaMemcpyAsync(w, &mine_ok, sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    const int r = rank_barrier(h, h->stream, ncclMin);
+    if (r) return r;
+    CUDA_TRY(h, cudaMemcpyAsync(all_ok, w, sizeof(float), cudaMemcpyDeviceToHost, h->stream));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+    return KREA_CUDA_OK;
+  };
+  float ok = 1.f;
   if (cudaMalloc(&d->sym, bytes) != cudaSuccess) {
     cudaGetLastError();
-    return fail(h, KREA_CUDA_E_NOMEM, "sequence-parallel workspace: cannot allocate %zu bytes", bytes);
+    d->sym = nullptr;
+    ok = 0.f;
+  }
+  float all_ok = 0.f;
+  if ((rc = agree(ok, &all_ok))) return rc;
+  if (all_ok < 0.5f) {
+    if (d->sym) cudaFree(d->sym);
+    d->sym = nullptr;
+    return fail(h, KREA_CUDA_E_NOMEM, "sequence-parallel workspace: a rank could not allocate %zu bytes", bytes);
   }
   d->sym_bytes = bytes;
   cudaIpcMemHandle_t mine, all[8];
@@ -232,7 +253,7 @@ static int sym_alloc(krea_cuda* h, size_t bytes) {
   NCCL_TRY(h, d, d->api->AllGather(d->xchg + d->rank * sizeof(mine), d->xchg, sizeof(mine), ncclInt8, d->comm, h->stream));
   CUDA_TRY(h, cudaMemcpyAsync(all, d->xchg, sizeof(mine) * d->nranks, cudaMemcpyDeviceToHost, h->stream));
   CUDA_TRY(h, cudaStreamSynchronize(h->stream));
-  float ok = 1.f;
+  ok = 1.f;
   for (int r = 0; r < d->nranks; r++) {
     if (r == d->rank) {
       d->peer[r] = d->sym;
@@ -242,13 +263,9 @@ static int sym_alloc(krea_cuda* h, size_t bytes) {
       ok = 0.f;
     }
   }
-  // every rank must take the same path afterwards: agree on the minimum
-  float* w = (float*)(d->xchg + 8 * sizeof(cudaIpcMemHandle_t));
-  CUDA_TRY(h, cudaMemcpyAsync(w, &ok, sizeof(ok), cudaMemcpyHostToDevice, h->stream));
-  if ((rc = rank_barrier(h, h->stream, ncclMin))) return rc;
-  CUDA_TRY(h, cudaMemcpyAsync(&ok, w, sizeof(ok), cudaMemcpyDeviceToHost, h->stream));
-  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
-  if (ok < 0.5f) {
+  // every rank must take the same path afterwards
+  if ((rc = agree(ok, &all_ok))) return rc;
+  if (all_ok < 0.5f) {
     close_peers(d);
     d->p2p = false;
   }

@@ -43,6 +43,7 @@ struct krea_cuda {
   bool profiling = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> marks[4];   // pending (start, stop) pairs per kind of work
   std::vector<cudaEvent_t> event_pool;
+  cudaEvent_t trace_base = nullptr;   // recorded by krea_cuda_profile_enable(h, 1): time zero of the trace file
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
   int gemm_bn = 0;                  // GEMM tile width: 0 = chosen per problem, 128 or 256 = forced
   int sm_count = 0;                 // SMs of the device (persistent kernels size their grid by it)

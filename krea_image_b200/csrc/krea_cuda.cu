@@ -99,6 +99,7 @@ void krea_cuda_destroy(krea_cuda* h) {
       cudaEventDestroy(m.second);
     }
   for (cudaEvent_t e : h->event_pool) cudaEventDestroy(e);
+  if (h->trace_base) cudaEventDestroy(h->trace_base);
   for (int i = 0; i < 18; i++)
     if (h->pipe_ev[i]) cudaEventDestroy(h->pipe_ev[i]);
   if (h->bounce) cudaFreeHost(h->bounce);
@@ -132,6 +133,38 @@ int krea_cuda_profile_enable(krea_cuda* h, int on) {
     h->marks[k].clear();
   }
   h->profiling = on != 0;
+  if (h->profiling) {
+    // time zero of krea_cuda_profile_trace
+    if (!h->trace_base) CUDA_TRY(h, cudaEventCreate(&h->trace_base));
+    CUDA_TRY(h, cudaEventRecord(h->trace_base, h->stream));
+  }
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_profile_trace(krea_cuda* h, const char* path) {
+  if (!h || !path) return fail(h, KREA_CUDA_E_ARG, "profile_trace: null handle or path");
+  if (!h->trace_base) return fail(h, KREA_CUDA_E_ARG, "profile_trace: profiling was never enabled");
+  CUDA_TRY(h, cudaSetDevice(h->device));
+  CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  FILE* f = fopen(path, "w");
+  if (!f) return fail(h, KREA_CUDA_E_ARG, "profile_trace: cannot open %s", path);
+  static const char* names[4] = {"qk_norm_rope", "attention", "exchange", "rank_barrier"};
+  fprintf(f, "{\"traceEvents\":[");
+  bool first = true;
+  for (int k = 0; k < 4; k++) {
+    for (auto& m : h->marks[k]) {
+      float t0 = 0.f, dt = 0.f;
+      if (cudaEventElapsedTime(&t0, h->trace_base, m.first) != cudaSuccess || cudaEventElapsedTime(&dt, m.first, m.second) != cudaSuccess) {
+        cudaGetLastError();
+        continue;
+      }
+      fprintf(f, "%s\n{\"name\":\"%s\",\"ph\":\"X\",\"pid\":%d,\"tid\":%d,\"ts\":%.3f,\"dur\":%.3f}", first ? "" : ",", names[k], h->device, k,
+              t0 * 1e3, dt * 1e3);
+      first = false;
+    }
+  }
+  fprintf(f, "\n]}\n");
+  fclose(f);
   return KREA_CUDA_OK;
 }
 

@@ -83,6 +83,10 @@ class KreaCuda:
         self._check(self.lib.krea_cuda_profile_read(self.h, which, ctypes.byref(ms), ctypes.byref(n)))
         return ms.value, n.value
 
+    def profile_trace(self, path):
+        """Chrome-trace JSON of the marks recorded since profile(True) (the reference's KREA_TRACE)."""
+        self._check(self.lib.krea_cuda_profile_trace(self.h, str(path).encode()))
+
     # ---- Metal::qk_norm_rope (engine/src/metal.h:80-82) ---------------------------------------------
     def qk_norm_rope(self, qkv, wq, wk, cos, sin, rows, ld, q_off, n_q, k_off, n_k, eps, mode=B.ROPE_PAIRS, big_dim=-1,
                      qbig=None, kbig=None):

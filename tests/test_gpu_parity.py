@@ -464,6 +464,27 @@ def test_tuning_knob_variants(monkeypatch, env):
         k2.close()
 
 
+def test_profile_marks_and_trace_file(kc, tmp_path):
+    """KREA_PROFILE / KREA_TRACE counterparts (engine/src/metal.h:126-145): per-kernel device times and a
+    Chrome-trace file with one complete event per bracketed launch."""
+    import json
+    H, T, gh, gw = 2, 32, 8, 8
+    S = T + gh * gw
+    qkv, wq, wk, cos, sin = rand_case(5, 1, S, H, T, gh, gw)
+    kc.profile(True)
+    for _ in range(3):
+        run_joint(kc, qkv, 1, S, H, wq, wk, cos, sin)
+    path = tmp_path / "trace.json"
+    kc.profile_trace(path)
+    ev = json.loads(path.read_text())["traceEvents"]
+    assert sorted(e["name"] for e in ev) == ["attention"] * 3 + ["qk_norm_rope"] * 3
+    assert all(e["ph"] == "X" and e["dur"] > 0 and e["ts"] >= 0 for e in ev)
+    ms, n = kc.profile_read(1)
+    assert n == 3 and ms > 0
+    assert abs(sum(e["dur"] for e in ev if e["name"] == "attention") / 1e3 - ms) < 1e-3 * max(ms, 1.0)
+    kc.profile(False)
+
+
 def test_argument_errors_launch_nothing(kc):
     n0 = kc.launches
     t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")

@@ -119,6 +119,7 @@ def run_reference(args, rank, world):
         print(json.dumps({"impl": "reference", "unavailable": "the reference's block runs on Metal only (unavailable on this box); its CPU restatement is a numpy statement sized for tests"}))
         return
     import oracle
+    oracle.set_num_threads(os.cpu_count() or 1)       # torchrun exports OMP_NUM_THREADS=1; this arm runs on one rank only
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
     heads_sel = list(range(0, cfg.heads, 6))          # 4 of 24 heads per step
     qkv = synth.qkv_slice(cfg, nb=1)

@@ -31,6 +31,11 @@ def _p(a, ty):
     return a.ctypes.data_as(ty)
 
 
+def set_num_threads(n: int) -> None:
+    """OpenMP threads the oracle may use from now on (a launcher may have exported OMP_NUM_THREADS=1)."""
+    lib().ko_set_num_threads(int(n))
+
+
 def num_threads() -> int:
     return int(lib().ko_num_threads())
 

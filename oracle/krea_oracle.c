@@ -52,6 +52,16 @@ static inline uint16_t f32_to_bf16(float x) {
 }
 static inline float bf16_round(float x) { return bf16_to_f32(f32_to_bf16(x)); }
 
+/* Launchers that start several ranks per node export OMP_NUM_THREADS=1; the benchmark's reference arm runs on one
+ * rank and wants every host thread, so it can say so. */
+void ko_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int ko_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

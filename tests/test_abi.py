@@ -98,3 +98,24 @@ def test_create_fails_loudly_without_a_device():
         assert "CUDA" in str(e) or "device" in str(e)
     else:
         raise AssertionError("krea_cuda_create must fail when there is no GPU (no CPU fallback)")
+
+
+def test_header_compiles_as_c_and_a_c_program_links(tmp_path):
+    """The boundary is a C ABI: a C11 translation unit including the header builds with -Wall -Werror -pedantic, links
+    against the library and gets sensible answers from the entry points that need no GPU."""
+    import subprocess
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from qw_writer import write_qw
+    lib = binding.library_path()
+    exe = tmp_path / "c_abi_smoke"
+    src = os.path.join(ROOT, "tests", "c_abi_smoke.c")
+    cmd = ["gcc", "-std=c11", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), src, "-o", str(exe),
+           "-L", os.path.dirname(lib), "-lkrea_cuda", "-lm", "-Wl,-rpath," + os.path.dirname(lib)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    qw = tmp_path / "w.qw"
+    write_qw(qw, [("L0.qn", "f32", np.full(128, 1.25, np.float32)), ("L0.kn", "f32", np.ones(128, np.float32))])
+    r = subprocess.run([str(exe), str(qw)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout + r.stderr
+    assert "L0.qn[0] = 1.250000, 2 tensors" in r.stdout

@@ -497,9 +497,25 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
       const int pos = p.q_row0 + row;
       const bool padded_row = pos >= pad_lo && pos < pad_hi;
-      const int rs = min(row, p.Lq - 1);
-      const uint4* gsrc = p.G ? (const uint4*)(p.G + (size_t)b * p.bsg + (size_t)rs * p.ldg + (size_t)h * D) + part * (16 / SPLIT) : nullptr;
       uint8_t* ostage = q_smem + g * TILE_BYTES;
+      // The gate rows of this tile are fetched the way the output leaves - 16 lanes per row, whole 256-byte rows per
+      // warp instruction - into a K/V stage nobody needs any more, and each thread then reads its own row from shared
+      // memory: 32 lanes each fetching 16 bytes of a different row from global memory cost the kernel several percent.
+      // Free stages: every MMA up to this tile's last P V has completed, so the stages of key tile n-2 are idle (the
+      // other query tile's last P V only reads the stage of V_{n-1}), and the producer has issued its last load.
+      uint8_t* gstage = kv_smem + ((2 * n_tiles + g) % NSTAGE) * TILE_BYTES;
+      if (p.G) {
+        const int sub = lane >> 4, gch = lane & 15;
+        constexpr int ROWS_PER_WARP = BM / C::SM_WARPS;
+        const __nv_bfloat16* gbase = p.G + (size_t)b * p.bsg + (size_t)h * D + 8 * gch;
+#pragma unroll 4
+        for (int it = 0; it < ROWS_PER_WARP / 2; it++) {
+          const int rr = wt * ROWS_PER_WARP + it * 2 + sub;
+          const int grow = min(q0 + g * BM + rr, p.Lq - 1);
+          *(uint4*)(gstage + rr * 256 + ((gch ^ (rr & 15)) << 4)) = __ldg((const uint4*)(gbase + (size_t)grow * p.ldg));
+        }
+        named_barrier(bar_id, C::SM_THREADS);
+      }
 #pragma unroll 1   // executed once per CTA: compact code beats unrolled code that has to be fetched cold
       for (int c0 = 0; c0 < D / SPLIT; c0 += 32) {
         uint32_t ov[32];
@@ -510,8 +526,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; e++) f[e] = padded_row ? 0.f : __uint_as_float(ov[q4 * 8 + e]) * inv;
-          if (gsrc) {
-            const uint4 gv = __ldg(gsrc + (c0 >> 3) + q4);
+          if (p.G) {
+            const uint4 gv = *(const uint4*)(gstage + r * 256 + (((part * (16 / SPLIT) + (c0 >> 3) + q4) ^ (r & 15)) << 4));
             const uint32_t g4[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
             for (int e = 0; e < 4; e++) {

@@ -40,6 +40,7 @@ struct AttnParams {
   __nv_bfloat16* O_blk[8];
   int o_blk_rows;
   int o_tma;                   // 1: the output tiles leave shared memory as TMA stores through the O tensor map
+  int q_tma;                   // 1 (only without a Q prologue): the Q tiles are TMA loads through the Q tensor map
   // 1: launch with programmatic stream serialisation, so that barrier set-up, TMEM allocation and Q staging
   // overlap the tail of the previous kernel in the stream (the K pre-pass).  Only for callers whose Q,
   // tables and weights do not come from that previous kernel: K, V and the logit bound are read after
@@ -53,8 +54,9 @@ struct AttnParams {
 // 128-byte swizzle.  split = threads per query row in the softmax (1 or 2); emu = 1 lets one of every four
 // element pairs evaluate exp2 with the FMA-pipe polynomial instead of the special-function unit.
 // O is described the same way when p.o_tma is set (its rows past Lq are clipped by the map).
-cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const AttnParams& p, int split,
-                                   int emu, cudaStream_t stream);
+// ... and Q when p.q_tma is set.
+cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const CUtensorMap& tmQ, const AttnParams& p,
+                                   int split, int emu, cudaStream_t stream);
 
 // Out-of-place / in-place per-head RMSNorm + RoPE (qk_norm_rope.cu).
 struct NormRopeParams {

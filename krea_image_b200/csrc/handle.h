@@ -34,6 +34,7 @@ struct krea_cuda {
   int split = 1;                    // softmax threads per query row
   int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
   bool pdl = true;                  // fused call: pre-pass and attention use programmatic dependent launch
+  bool q_tma = true;                // plain attention operator: Q tiles arrive as TMA loads
   bool o_tma = true;                // attention output tiles leave shared memory as TMA stores
   bool static_bound = true;         // let the fused call replace the running max by the QK-norm logit bound
   cudaStream_t copy_in = nullptr, copy_out = nullptr;   // host entry point: H2D and D2H streams

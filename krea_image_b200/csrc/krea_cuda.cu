@@ -72,6 +72,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
   if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_O_TMA")) h->o_tma = atoi(s) != 0;                 // tuning knob
+  if (const char* s = getenv("KREA_CUDA_Q_TMA")) h->q_tma = atoi(s) != 0;                 // tuning knob
   if (const char* s = getenv("KREA_CUDA_GEMM_BN")) {                                      // tuning knob: GEMM tile width
     const int v = atoi(s);
     if (v == 128 || v == 256) h->gemm_bn = v;
@@ -326,10 +327,17 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
     p.o_blk_rows = c.o_blk_rows;
   }
 
-  CUtensorMap tmK, tmV, tmO;
+  CUtensorMap tmK, tmV, tmO, tmQ;
   memset(&tmK, 0, sizeof(tmK));
   memset(&tmV, 0, sizeof(tmV));
   memset(&tmO, 0, sizeof(tmO));
+  memset(&tmQ, 0, sizeof(tmQ));
+  if (h->q_tma && c.wq == nullptr && c.Lk > 0) {
+    // no prologue: Q goes from global to the MMA's shared-memory layout by TMA, no thread touches it
+    int rc = make_kv_map(h, &tmQ, c.Q, c.heads * 128, c.Lq, c.batch, c.ldq, c.bsq, "Q");
+    if (rc) return rc;
+    p.q_tma = 1;
+  }
   if (h->o_tma && c.o_blk == nullptr && c.Lk > 0) {
     // the output leaves shared memory as TMA tile stores (not with the row-block scatter, whose rows have several bases)
     int rc = make_kv_map(h, &tmO, c.O, c.heads * 128, c.Lq, c.batch, c.ldo, c.bso, "O");
@@ -344,7 +352,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   }
   {
     ProfileMark pm(h, 1);
-    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, p, h->split, h->emu, h->stream));
+    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, tmQ, p, h->split, h->emu, h->stream));
   }
   h->launches++;
   return KREA_CUDA_OK;

@@ -485,6 +485,33 @@ def test_profile_marks_and_trace_file(kc, tmp_path):
     kc.profile(False)
 
 
+def test_plain_operator_q_by_tma_matches_staged_q(kc, monkeypatch):
+    """Without a prologue the Q tiles arrive by TMA; staging them through registers instead (the knob) puts the same
+    bytes in shared memory, so the outputs are bit-identical - ragged Lq, GQA and a batch included."""
+    rng = np.random.default_rng(99)
+    B, Lq, Lk, H, group = 2, 333, 450, 4, 2
+    kvh = H // group
+    mk = lambda *shape: synth.f32_to_bf16_bits(rng.standard_normal(shape).astype(np.float32)).reshape(shape)
+    Q, K, V = mk(B, Lq, H * 128), mk(B, Lk, kvh * 128), mk(B, Lk, kvh * 128)
+    outs = []
+    monkeypatch.setenv("KREA_CUDA_Q_TMA", "0")
+    k2 = ops.KreaCuda(0)
+    try:
+        k2.set_stream(torch.cuda.current_stream())
+        for handle in (kc, k2):
+            o = torch.zeros((B, Lq, H * 128), dtype=torch.bfloat16, device="cuda")
+            handle.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, H * 128, kvh * 128, kvh * 128, H * 128, group,
+                             batch=B, bsq=Lq * H * 128, bsk=Lk * kvh * 128, bsv=Lk * kvh * 128, bso=Lq * H * 128)
+            handle.wait()
+            outs.append(o)
+    finally:
+        k2.close()
+    assert torch.equal(outs[0], outs[1])
+    for b in range(B):
+        want = oracle.attention(Q[b].reshape(-1), K[b].reshape(-1), V[b].reshape(-1), Lq, Lk, H, H * 128, kvh * 128, kvh * 128, group=group)
+        check(host_f32(outs[0][b]), want, None, f"plain operator, sample {b}")
+
+
 def test_argument_errors_launch_nothing(kc):
     n0 = kc.launches
     t = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")

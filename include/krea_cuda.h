@@ -225,7 +225,7 @@ KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwi
  * row); the attention is then called through krea_cuda_attention on the result.
  * KREA_CUDA_EPI_RESID_GATE / _SWIGLU are the epilogues of the O-projection and of the MLP (model.mm:357-366).
  * int8 weights (Weight::q8) are dequantised once with krea_cuda_dequant_q8 and then used as bf16.  Not built: the
- * LoRA term and the column remap (seg): they have no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * column remap (seg): it has no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
  * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
 #define KREA_CUDA_EPI_BF16 0
 #define KREA_CUDA_EPI_QKNORM_ROPE 1
@@ -257,6 +257,12 @@ typedef struct {
   int big_dim;
   float* qbig;
   float* kbig;
+  /* optional second product accumulated before the epilogue (the reference's LoraTerm, engine/src/metal.h:31-35,
+   * gemm.metal:46-50): acc += lora_A[M, lora_K] x lora_W[lora_K, N], both bf16; NULL = none.  lora_K, lora_lda and
+   * lora_ldw multiples of 8. */
+  const void* lora_A;
+  const void* lora_W;
+  int lora_K, lora_lda, lora_ldw;
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
 

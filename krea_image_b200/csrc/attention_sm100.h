@@ -138,6 +138,7 @@ struct GemmParams {
   __nv_bfloat16* C;
   int64_t ldc;
   int M, N, K;
+  int K2;                       // > 0: a second product A2[M, K2] x W2[K2, N] is accumulated before the epilogue
   int epi;                      // 0: bf16 store; 1: Q / K head blocks are RMS-normalised, weighted and rotated first;
                                 // 2: C is fp32 and receives += vec[col] * acc (vec nullptr: += acc); 3: SwiGLU, C has N / 2 columns;
                                 // 4: fp32 store; 5: gelu_tanh, bf16; 6: + vec[col], bf16; 7: + vec[col], fp32
@@ -163,6 +164,8 @@ struct GemmParams {
 };
 // A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.
 // force_bn: 0 = choose the tile width (256 or 128 columns) by how well the tiles fill the last wave; 128 / 256 = as told
-cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, int force_bn, cudaStream_t stream);
+// tmA2 / tmW2 describe the second product the same way (ignored when p.K2 == 0)
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
+                                   int sms, int force_bn, cudaStream_t stream);
 
 }  // namespace krea

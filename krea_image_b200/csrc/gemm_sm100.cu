@@ -45,7 +45,8 @@ struct Cfg {
 
 template <int BN>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
-gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
+gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA2,
+                const __grid_constant__ CUtensorMap tmW2, const GemmParams p) {
   using namespace gemm;
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
@@ -61,7 +62,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mt = (p.M + BM - 1) / BM, nt = (p.N + BN - 1) / BN;
-  const int tiles = mt * nt, kblocks = (p.K + BK - 1) / BK;
+  // the optional second product (A2 x W2, the reference's LoRA term, gemm.metal:46-50) is just more k-blocks
+  // accumulated into the same tile before the epilogue
+  const int kb1 = (p.K + BK - 1) / BK, kblocks = kb1 + (p.K2 + BK - 1) / BK;
+  const int tiles = mt * nt;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -102,6 +106,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmW);
+      if (p.K2 > 0) {
+        tma_prefetch_desc(&tmA2);
+        tma_prefetch_desc(&tmW2);
+      }
       uint32_t n = 0;     // k-blocks issued so far
       for (int t = blockIdx.x; t < tiles && *abort_word == 0u; t += gridDim.x) {
         int m0, n0;
@@ -112,9 +120,12 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_BYTES;
           mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-          tma_load_3d(a_dst, &tmA, &full[s], kb * BK, m0, 0);
+          const CUtensorMap* ma = kb < kb1 ? &tmA : &tmA2;
+          const CUtensorMap* mw = kb < kb1 ? &tmW : &tmW2;
+          const int k0 = (kb < kb1 ? kb : kb - kb1) * BK;
+          tma_load_3d(a_dst, ma, &full[s], k0, m0, 0);
 #pragma unroll
-          for (int j = 0; j < BN / 64; j++) tma_load_3d(b_dst + j * B_BLOCK, &tmW, &full[s], n0 + j * 64, kb * BK, 0);
+          for (int j = 0; j < BN / 64; j++) tma_load_3d(b_dst + j * B_BLOCK, mw, &full[s], n0 + j * 64, k0, 0);
         }
       }
       // nothing may still be in flight into this CTA's shared memory when it exits
@@ -373,7 +384,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 template <int BN>
-static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, cudaStream_t stream) {
+static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
+                                       int sms, cudaStream_t stream) {
   using namespace gemm;
   static bool configured[64] = {};
   int dev = 0;
@@ -385,11 +397,12 @@ static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_bf16_sm100<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(tmA, tmW, p);
+  gemm_bf16_sm100<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(tmA, tmW, tmA2, tmW2, p);
   return cudaGetLastError();
 }
 
-cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const GemmParams& p, int sms, int force_bn, cudaStream_t stream) {
+cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
+                                   int sms, int force_bn, cudaStream_t stream) {
   using namespace gemm;
   if (p.M <= 0 || p.N <= 0 || p.K <= 0) return cudaSuccess;
   // share of the CTAs' time slots that do work when the tiles are dealt out in waves of `sms`
@@ -401,7 +414,7 @@ cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tm
   // the narrow tile moves a third more bytes through shared memory per flop and measures ~20 % slower per tile
   // (1100 against 1340 TFLOP/s on full waves), so it has to fill the waves a good deal better to win
   const bool narrow = force_bn == 128 || (force_bn != 256 && wave_eff(128) > wave_eff(256) * 1.3);
-  return narrow ? launch_gemm_variant<128>(tmA, tmW, p, sms, stream) : launch_gemm_variant<256>(tmA, tmW, p, sms, stream);
+  return narrow ? launch_gemm_variant<128>(tmA, tmW, tmA2, tmW2, p, sms, stream) : launch_gemm_variant<256>(tmA, tmW, tmA2, tmW2, p, sms, stream);
 }
 
 }  // namespace krea

@@ -812,16 +812,26 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
     }
   }
   CUDA_TRY(h, cudaSetDevice(h->device));
-  CUtensorMap tmA, tmW;
+  CUtensorMap tmA, tmW, tmA2, tmW2;
+  memset(&tmA2, 0, sizeof(tmA2));
+  memset(&tmW2, 0, sizeof(tmW2));
   int rc = make_kv_map(h, &tmA, a->A, a->K, a->M, 1, a->lda, 0, "A", 128);
   if (rc) return rc;
   if ((rc = make_kv_map(h, &tmW, a->W, a->N, a->K, 1, a->ldw, 0, "W", 64))) return rc;
+  if (a->lora_A || a->lora_W) {
+    if (!a->lora_A || !a->lora_W || !aligned16(a->lora_A) || !aligned16(a->lora_W) || a->lora_K <= 0 || a->lora_K % 8 || a->lora_lda % 8 || a->lora_ldw % 8 ||
+        a->lora_lda < a->lora_K || a->lora_ldw < a->N)
+      return fail(h, KREA_CUDA_E_ARG, "gemm: bad second (LoRA) product");
+    if ((rc = make_kv_map(h, &tmA2, a->lora_A, a->lora_K, a->M, 1, a->lora_lda, 0, "lora A", 128))) return rc;
+    if ((rc = make_kv_map(h, &tmW2, a->lora_W, a->N, a->lora_K, 1, a->lora_ldw, 0, "lora W", 64))) return rc;
+    p.K2 = a->lora_K;
+  }
   if (h->sm_count == 0) {
     cudaDeviceProp prop;
     CUDA_TRY(h, cudaGetDeviceProperties(&prop, h->device));
     h->sm_count = prop.multiProcessorCount;
   }
-  CUDA_TRY(h, launch_gemm_bf16_sm100(tmA, tmW, p, h->sm_count, h->gemm_bn, h->stream));
+  CUDA_TRY(h, launch_gemm_bf16_sm100(tmA, tmW, tmA2, tmW2, p, h->sm_count, h->gemm_bn, h->stream));
   h->launches++;
   return KREA_CUDA_OK;
 }

@@ -189,6 +189,39 @@ def test_gemm_remaining_epilogues(kc, epi):
             kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N + 8, epilogue=code)          # bias vector missing
 
 
+@pytest.mark.parametrize("rank,epi", [(16, "bf16"), (40, "swiglu"), (128, "resid")])
+def test_gemm_second_product_lora_term(kc, rank, epi):
+    """LoraTerm (metal.h:31-35, gemm.metal:46-50): acc += A2[M, K2] x W2[K2, N] before the epilogue, so the fused
+    epilogues see the full result."""
+    M, N, K = 260, 384, 200
+    a, w = _case(71, M, N, K, K, N)
+    rng = np.random.default_rng(72 + rank)
+    a2 = _bits(rng.standard_normal((M, rank)))
+    w2 = _bits(rng.standard_normal((rank, N)) / np.sqrt(rank))
+    acc = (synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+           + synth.bf16_bits_to_f32(a2).astype(np.float64) @ synth.bf16_bits_to_f32(w2).astype(np.float64))
+    lora = (_dev(a2), _dev(w2), rank, rank, N)
+    if epi == "bf16":
+        c = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+        kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N, lora=lora)
+        want = acc
+    elif epi == "swiglu":
+        c = torch.zeros((M, N // 2), dtype=torch.bfloat16, device="cuda")
+        kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N // 2, epilogue=binding.EPI_SWIGLU, lora=lora)
+        g = acc.reshape(M, N // 64, 2, 32)
+        want = (g[:, :, 0] / (1.0 + np.exp(-g[:, :, 0])) * g[:, :, 1]).reshape(M, N // 2)
+    else:
+        x0 = rng.standard_normal((M, N)).astype(np.float32)
+        c = torch.from_numpy(x0).cuda()
+        kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N, epilogue=binding.EPI_RESID_GATE, lora=lora)
+        want = x0 + acc
+    kc.wait()
+    rel, mx = _rel(c.float().cpu().numpy(), want)
+    assert rel <= 3e-3, f"rel-L2 {rel:.3e} max-abs {mx:.3e}"
+    with pytest.raises(ops.KreaCudaError):
+        kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N, lora=(_dev(a2), None, rank, rank, N))
+
+
 def _q8(w):
     """tools/convert.py:92-99: symmetric int8 per output column and group of 128 input rows."""
     K, N = w.shape

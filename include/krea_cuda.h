@@ -224,8 +224,8 @@ KREA_CUDA_API int krea_cuda_layerwise_attn(krea_cuda* h, const krea_cuda_layerwi
  * the projection writes Q and K already normalised and rotated (rope_mode 0 or 2; cos/sin row = row0 + output
  * row); the attention is then called through krea_cuda_attention on the result.
  * KREA_CUDA_EPI_RESID_GATE / _SWIGLU are the epilogues of the O-projection and of the MLP (model.mm:357-366).
- * int8 weights (Weight::q8) are dequantised once with krea_cuda_dequant_q8 and then used as bf16.  Not built: the
- * column remap (seg): it has no field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
+ * int8 weights (Weight::q8) are dequantised once with krea_cuda_dequant_q8 and then used as bf16.  Every
+ * epilogue, the LoRA term and the column remap of the reference's kernel have a field here.  Pointers 16-byte aligned; lda, ldw, ldc, N, q_off and
  * k_off multiples of 8 (q_off, k_off of 128 with the fused epilogue). */
 #define KREA_CUDA_EPI_BF16 0
 #define KREA_CUDA_EPI_QKNORM_ROPE 1
@@ -263,6 +263,9 @@ typedef struct {
   const void* lora_A;
   const void* lora_W;
   int lora_K, lora_lda, lora_ldw;
+  /* EPI_BF16 only, optional column remap (GemmParams::seg, gemm.metal:41-43): output column n is stored at column
+   * (n / seg) * seg_stride + n % seg; seg and seg_stride multiples of 8, 0 = off.  ldc must cover the last segment. */
+  int seg, seg_stride;
 } krea_cuda_gemm_args;
 KREA_CUDA_API int krea_cuda_gemm(krea_cuda* h, const krea_cuda_gemm_args* a);
 

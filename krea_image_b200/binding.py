@@ -62,7 +62,8 @@ class GemmArgs(ctypes.Structure):
                 ("q_off", _int), ("n_q", _int), ("k_off", _int), ("n_k", _int),
                 ("wq", _vp), ("wk", _vp), ("cos", _vp), ("sin", _vp), ("row0", _int), ("eps", ctypes.c_float), ("rope_mode", _int), ("vec", _vp),
                 ("big_dim", _int), ("qbig", _vp), ("kbig", _vp),
-                ("lora_A", _vp), ("lora_W", _vp), ("lora_K", _int), ("lora_lda", _int), ("lora_ldw", _int)]
+                ("lora_A", _vp), ("lora_W", _vp), ("lora_K", _int), ("lora_lda", _int), ("lora_ldw", _int),
+                ("seg", _int), ("seg_stride", _int)]
 
 
 class DequantArgs(ctypes.Structure):

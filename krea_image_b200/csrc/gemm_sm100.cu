@@ -359,8 +359,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int q4 = 0; q4 < 4; q4++) {
               const int col = col0 + c0 + q4 * 8;
+              // optional column remap of the plain store (gemm.metal:41-43, 255-256): segments of `seg` columns land
+              // seg_stride apart; seg is a multiple of 8, so an 8-column chunk never straddles two segments
+              const int ocol = p.seg > 0 ? (col / p.seg) * p.seg_stride + col % p.seg : col;
               if (col + 8 <= p.N)
-                *(uint4*)(crow + col) = make_uint4(pack_bf16x2(f[q4 * 8], f[q4 * 8 + 1]), pack_bf16x2(f[q4 * 8 + 2], f[q4 * 8 + 3]),
+                *(uint4*)(crow + ocol) = make_uint4(pack_bf16x2(f[q4 * 8], f[q4 * 8 + 1]), pack_bf16x2(f[q4 * 8 + 2], f[q4 * 8 + 3]),
                                                    pack_bf16x2(f[q4 * 8 + 4], f[q4 * 8 + 5]), pack_bf16x2(f[q4 * 8 + 6], f[q4 * 8 + 7]));
             }
           }

@@ -779,7 +779,10 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
   const bool has_bias = a->epilogue == KREA_CUDA_EPI_BIAS_BF16 || a->epilogue == KREA_CUDA_EPI_BIAS_F32;
   if (has_bias && (!a->vec || !aligned16(a->vec))) return fail(h, KREA_CUDA_E_ARG, "gemm: the bias vector is missing or misaligned");
   const int out_cols = a->epilogue == KREA_CUDA_EPI_SWIGLU ? a->N / 2 : a->N;
-  if (a->lda < a->K || a->ldw < a->N || a->ldc < out_cols) return fail(h, KREA_CUDA_E_ARG, "gemm: a leading dimension is smaller than its row");
+  if (a->seg < 0 || a->seg_stride < 0 || a->seg % 8 || a->seg_stride % 8 || (a->seg > 0 && (a->epilogue != KREA_CUDA_EPI_BF16 || a->seg_stride < a->seg)))
+    return fail(h, KREA_CUDA_E_ARG, "gemm: the column remap needs the bf16 epilogue, seg and seg_stride multiples of 8 and seg_stride >= seg");
+  const int out_span = a->seg > 0 ? ((a->N - 1) / a->seg) * a->seg_stride + (a->N - 1) % a->seg + 1 : out_cols;
+  if (a->lda < a->K || a->ldw < a->N || a->ldc < out_span) return fail(h, KREA_CUDA_E_ARG, "gemm: a leading dimension is smaller than its row");
   if (a->epilogue == KREA_CUDA_EPI_SWIGLU && a->N % 64) return fail(h, KREA_CUDA_E_ARG, "gemm: SwiGLU needs N to be a multiple of 64 (32 gate + 32 up columns per group)");
   if (a->epilogue == KREA_CUDA_EPI_RESID_GATE && !aligned16(a->vec)) return fail(h, KREA_CUDA_E_ARG, "gemm: the gate vector must be 16-byte aligned");
   GemmParams p{};
@@ -788,6 +791,7 @@ static int gemm_impl(krea_cuda* h, const krea_cuda_gemm_args* a, float* bound_ou
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.status = h->status_dev;
   p.epi = a->epilogue;
+  p.seg = a->seg; p.seg_stride = a->seg_stride;
   p.vec = (a->epilogue == KREA_CUDA_EPI_RESID_GATE || has_bias) ? a->vec : nullptr;
   if (a->epilogue == KREA_CUDA_EPI_QKNORM_ROPE) {
     if (a->rope_mode == KREA_CUDA_ROPE_HALF) return fail(h, KREA_CUDA_E_UNSUPPORTED, "gemm: the fused epilogue rotates interleaved pairs only (rope_mode 0 or 2)");

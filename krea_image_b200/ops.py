@@ -140,7 +140,7 @@ class KreaCuda:
         a.Lk, a.heads, a.group, a.batch = Lk, heads, group, batch
         return int(self.lib.krea_cuda_joint_scratch_bytes(ctypes.byref(a)))
 
-    def gemm(self, A, W, C, M, N, K, lda, ldw, ldc, *, qk_norm=None, epilogue=B.EPI_BF16, vec=None, lora=None):
+    def gemm(self, A, W, C, M, N, K, lda, ldw, ldc, *, qk_norm=None, epilogue=B.EPI_BF16, vec=None, lora=None, seg=0, seg_stride=0):
         """Metal::gemm with Epi::BF16 (engine/src/metal.h:64-67): C[M,N] = A[M,K] x Wt[K,N], bf16.
         qk_norm = dict(q_off, n_q, k_off, n_k, wq, wk, cos, sin, row0, eps, rope_mode) fuses Metal::qk_norm_rope
         on those head blocks into the store.  epilogue = B.EPI_RESID_GATE: C is f32 and receives += vec[n] * acc
@@ -149,6 +149,7 @@ class KreaCuda:
         a.A, a.W, a.C = _ptr(A), _ptr(W), _ptr(C)
         a.M, a.N, a.K, a.lda, a.ldw, a.ldc = M, N, K, lda, ldw, ldc
         a.epilogue, a.vec = epilogue, _ptr(vec)
+        a.seg, a.seg_stride = seg, seg_stride
         if lora is not None:      # (A2, W2, K2, lda2, ldw2): acc += A2 x W2 before the epilogue (metal.h:31-35 LoraTerm)
             a.lora_A, a.lora_W, a.lora_K, a.lora_lda, a.lora_ldw = _ptr(lora[0]), _ptr(lora[1]), lora[2], lora[3], lora[4]
         if qk_norm is not None:

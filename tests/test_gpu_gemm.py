@@ -222,6 +222,27 @@ def test_gemm_second_product_lora_term(kc, rank, epi):
         kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, N, lora=(_dev(a2), None, rank, rank, N))
 
 
+def test_gemm_column_remap(kc):
+    """GemmParams::seg (gemm.metal:41-43): segments of `seg` output columns land `seg_stride` apart - the reference
+    uses it to drop the GPU's slice of a head-split projection into a wider row."""
+    M, N, K, seg, stride = 130, 384, 72, 128, 200
+    a, w = _case(81, M, N, K, K, N)
+    acc = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
+    ldc = 2 * stride + seg + 8
+    c = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, ldc, seg=seg, seg_stride=stride)
+    kc.wait()
+    got = c.float().cpu().numpy()
+    touched = np.zeros(ldc, dtype=bool)
+    for s0 in range(N // seg):
+        rel, _ = _rel(got[:, s0 * stride:s0 * stride + seg], acc[:, s0 * seg:(s0 + 1) * seg])
+        assert rel <= 3e-3
+        touched[s0 * stride:s0 * stride + seg] = True
+    assert np.all(np.isnan(got[:, ~touched]))
+    with pytest.raises(ops.KreaCudaError):
+        kc.gemm(_dev(a), _dev(w), c, M, N, K, K, N, 2 * stride, seg=seg, seg_stride=stride)      # ldc does not cover the last segment
+
+
 def _q8(w):
     """tools/convert.py:92-99: symmetric int8 per output column and group of 128 input rows."""
     K, N = w.shape

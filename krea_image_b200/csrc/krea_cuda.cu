@@ -560,7 +560,22 @@ static int stage_buf(krea_cuda* h, int slot, size_t bytes, void** out) {
   return KREA_CUDA_OK;
 }
 
+static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a);
+
 int krea_cuda_joint_attention_host(krea_cuda* h, const krea_cuda_joint_args* a) {
+  const int rc = host_pipeline(h, a);
+  if (rc != KREA_CUDA_OK && h) {
+    // A failure part-way leaves copies from and to the caller's buffers in flight: let them finish before the
+    // caller gets its buffers back.  The error already recorded in the handle stays the one reported.
+    if (h->copy_in) cudaStreamSynchronize(h->copy_in);
+    cudaStreamSynchronize(h->stream);
+    if (h->copy_out) cudaStreamSynchronize(h->copy_out);
+    cudaGetLastError();
+  }
+  return rc;
+}
+
+static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
   int rc = validate_joint(h, a);
   if (rc) return rc;
   if (!a->Q || !a->O) return fail(h, KREA_CUDA_E_ARG, "joint_attention_host: null tensor");

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the joint text+image attention path (QK-RMSNorm + RoPE prologue + attention).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2|c3] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c0|c2|c3|c4|block|gemm|layerwise] [--impl ours|reference]
 
 One "step" = one pass of the path over one batch: the library's fused call (K pre-pass + attention
 kernel with the Q prologue fused) on seeded synthetic inputs of the named configuration.  Default
@@ -17,6 +17,9 @@ roofline the attention kernel alone (CUDA events around each launch) against the
 cpu_baseline  the CPU oracle (fp32) on this machine's cores, rank 0 at N=1 only
 --impl reference  times that CPU implementation instead (the reference has no other runnable code
          for this path off macOS)
+--workload c4 is the long-sequence configuration (sequence-parallel over the GPUs); block, gemm and
+         layerwise time the kernels either side of the attention (a whole DiT block, its q|k|v|gate
+         projection, the text fusion's 12-tap attention), each with its own metric and roofline.
 """
 import argparse
 import json
@@ -50,6 +53,17 @@ def measured_peaks():
         except Exception:
             pass
     return FALLBACK_PEAK_TFLOPS, 1400.0, "fallback"
+
+
+def measured_hbm_peak():
+    """(GB/s of the measured copy peak, its kind)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured copy bandwidth"
+        except Exception:
+            pass
+    return 6650.0, "fallback copy bandwidth"
 
 
 class ClockSampler:
@@ -115,8 +129,8 @@ def run_reference(args, rank, world):
     reference itself is Metal-only), timed with every host thread on a bounded sample per step."""
     if rank != 0:
         return
-    if args.workload == "block":
-        print(json.dumps({"impl": "reference", "unavailable": "the reference's block runs on Metal only (unavailable on this box); its CPU restatement is a numpy statement sized for tests"}))
+    if args.workload in ("block", "gemm", "layerwise"):
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's {args.workload} runs on Metal only (unavailable on this box); its CPU restatement is sized for tests, not timed"}))
         return
     import oracle
     oracle.set_num_threads(os.cpu_count() or 1)       # torchrun exports OMP_NUM_THREADS=1; this arm runs on one rank only
@@ -327,6 +341,104 @@ def run_block(args, rank, world, local_rank):
     kc.close()
 
 
+def run_kernel_workload(args, rank, world, local_rank):
+    """--workload gemm | layerwise: the two other kernels either side of the attention, each timed alone on inputs
+    larger than L2.  gemm: the block's q|k|v|gate projection at the reference model's width (4608 x 15360 x 6144,
+    bf16) with the fused QK-norm + RoPE epilogue, the plain store and the library GEMM beside it.  layerwise: the
+    text fusion's 12-tap attention (engine/kernels/norm.metal:136-178) over 4096 tokens x 20 heads, HBM-bound."""
+    import torch
+    import torch.distributed as dist
+
+    from krea_image_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    kc = ops.KreaCuda(local_rank)
+    stream = torch.cuda.current_stream()
+    kc.set_stream(stream)
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    extra = {}
+
+    def timed(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return e0.elapsed_time(e1) / steps
+
+    warmup = max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    if args.workload == "gemm":
+        M, K, heads, kv = 4608, 6144, 48, 12
+        N = (2 * heads + 2 * kv) * 128
+        A = [torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(2)]
+        Wt = [(torch.randn(K, N, device="cuda", generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(2)]
+        C = [torch.empty(M, N, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        wq, wk = (torch.rand(128, device="cuda", generator=g) + 0.5 for _ in range(2))
+        cos_h, sin_h = ops.rope_tables_axial2d(512, 64, 64)
+        cos, sin = torch.from_numpy(cos_h).cuda(), torch.from_numpy(sin_h).cuda()
+        qk = dict(q_off=0, n_q=heads, k_off=heads * 128, n_k=kv, wq=wq, wk=wk, cos=cos, sin=sin)
+        if rank == 0:
+            sampler.start()
+        n0 = kc.launches
+        ms = timed(lambda i: kc.gemm(A[i & 1], Wt[i & 1], C[i & 1], M, N, K, K, N, N, qk_norm=qk), args.steps, warmup)
+        launches = kc.launches - n0 - warmup
+        clocks = sampler.stop() if rank == 0 else None
+        ms_plain = timed(lambda i: kc.gemm(A[i & 1], Wt[i & 1], C[i & 1], M, N, K, K, N, N), args.steps, warmup)
+        ms_lib = timed(lambda i: torch.matmul(A[i & 1], Wt[i & 1], out=C[i & 1]), args.steps, warmup)
+        work = 2.0 * M * N * K
+        unit, scale, bound = "TFLOP/s", 1e12, "tensor"
+        metric = "q|k|v|gate projection TFLOP/s, 4608 x 15360 x 6144 bf16, fused QK-norm + RoPE epilogue"
+        config = {"workload": "qkvg-projection-1024sq", "M": M, "N": N, "K": K, "epilogue": "QKNORM_ROPE",
+                  "l2": "two rotating operand sets (387 MB each > 126 MB L2)", "flops_per_step_per_gpu": work}
+        extra = {"plain_store_tflops": work / ms_plain / 1e9, "library_gemm_tflops": work / ms_lib / 1e9,
+                 "library_gemm": "torch.matmul (cuBLAS), same process, same operands"}
+        kernel, traffic = "gemm_bf16_sm100<256>", None
+    else:
+        T, H = 4096, 20
+        rows, ld = T * 12, 4 * H * 128
+        X = [torch.randn(rows, ld, device="cuda", generator=g).to(torch.bfloat16) for _ in range(2)]
+        O = torch.empty(rows, H * 128, dtype=torch.bfloat16, device="cuda")
+        if rank == 0:
+            sampler.start()
+        n0 = kc.launches
+        ms = timed(lambda i: kc.layerwise_attn(X[i & 1], O, rows, ld, H * 128, H, 0, H * 128, 2 * H * 128, 3 * H * 128), args.steps, warmup)
+        launches = kc.launches - n0 - warmup
+        clocks = sampler.stop() if rank == 0 else None
+        work = rows * H * 128 * 2 * 5.0           # q, k, v and gate rows read once, the output row written once
+        unit, scale, bound = "GB/s", 1e9, "hbm"
+        metric = "layerwise (12-tap) attention GB/s, 4096 tokens x 20 heads, head_dim 128"
+        config = {"workload": "layerwise-4096tok", "tokens": T, "taps": 12, "heads": H, "head_dim": 128,
+                  "l2": "two rotating inputs (1007 MB each > 126 MB L2)", "bytes_per_step_per_gpu": work}
+        kernel, traffic = "layerwise_attn_kernel", None
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        peak_tf, _, peak_kind = measured_peaks()
+        peak = peak_tf if bound == "tensor" else measured_hbm_peak()[0]
+        if bound == "hbm":
+            peak_kind = measured_hbm_peak()[1]
+        per_gpu = work / (ms * 1e-3) / scale
+        print(json.dumps({
+            "metric": metric, "value": world * per_gpu, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": config, "gpu_launches": int(launches), "clocks": clocks, "e2e": None,
+            "roofline": {"bound": bound, "achieved": per_gpu, "peak": peak, "unit": unit, "frac": per_gpu / peak, "traffic": traffic,
+                         "peak_kind": peak_kind, "kernel": kernel}, **extra}))
+    kc.close()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -337,6 +449,8 @@ def run_ours(args, rank, world, local_rank):
         return run_seq_parallel(args, rank, world, local_rank)
     if args.workload == "block":
         return run_block(args, rank, world, local_rank)
+    if args.workload in ("gemm", "layerwise"):
+        return run_kernel_workload(args, rank, world, local_rank)
     torch.cuda.set_device(local_rank)
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
     B, S, H = cfg.batch, cfg.seq, cfg.heads
@@ -483,7 +597,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["block"])
+    ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["block", "gemm", "layerwise"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--shard", default="samples", choices=["samples", "heads"],
                     help="several GPUs, workloads c0-c3: every GPU runs a whole problem (weak scaling), or its share of the heads of one problem (strong)")

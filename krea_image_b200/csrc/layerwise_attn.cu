@@ -11,7 +11,8 @@
 // 16 x 16 x 128 product on the warp-level tensor-core path (mma.sync m16n8k16, bf16 in, fp32 accumulate;
 // rows and columns 12-15 are padding whose results are dropped): a 12-key problem is far too small for a
 // tcgen05 tile, and on CUDA cores the bf16 -> fp32 conversions of the score phase made the kernel
-// issue-bound at a third of the HBM rate.
+// issue-bound at a third of the HBM rate.  The weighted sum runs on packed two-wide fp32 multiply-adds (the taps in
+// order, so the values are those of a scalar sum).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -40,7 +41,9 @@ __device__ __forceinline__ void mma_m16n8k16_bf16(float (&d)[4], const uint32_t 
 
 __global__ void __launch_bounds__(LW_WARPS * 32) layerwise_attn_kernel(const LayerwiseParams p) {
   __shared__ __align__(16) uint8_t tiles[LW_WARPS][2][LW_TILE];
-  __shared__ float probs[LW_WARPS][TAPS][TAPS + 1];
+  // probabilities, each stored twice in a row (p, p): a 16-byte load then yields two ready operands of the packed
+  // two-wide multiply-add
+  __shared__ __align__(16) float probs[LW_WARPS][TAPS][2 * TAPS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tokens = p.rows / TAPS;
   const long long units = (long long)tokens * p.heads;
@@ -111,11 +114,12 @@ __global__ void __launch_bounds__(LW_WARPS * 32) layerwise_attn_kernel(const Lay
         const float inv = 1.0f / l;
         const int row = g + 8 * half;
         if (row < TAPS) {
-          probs[warp][row][2 * t] = e0 * inv;
-          probs[warp][row][2 * t + 1] = e1 * inv;
+          float4* prow = (float4*)&probs[warp][row][0];
+          const float p0 = e0 * inv, p1 = e1 * inv;
+          prow[t] = make_float4(p0, p0, p1, p1);                        // key columns 2t, 2t + 1
           if (hi_ok) {
-            probs[warp][row][8 + 2 * t] = e2 * inv;
-            probs[warp][row][9 + 2 * t] = e3 * inv;
+            const float p2 = e2 * inv, p3 = e3 * inv;
+            prow[4 + t] = make_float4(p2, p2, p3, p3);                  // key columns 8 + 2t, 9 + 2t
           }
         }
       }
@@ -123,22 +127,28 @@ __global__ void __launch_bounds__(LW_WARPS * 32) layerwise_attn_kernel(const Lay
     __syncwarp();
     // ---- weighted sum, gate, store: lane owns channels 4*lane .. 4*lane+3 of every row ----
     {
-      float v[TAPS][4];
+      uint64_t v2[TAPS][2];                             // channels (0, 1) and (2, 3) of every value row as fp32 pairs
 #pragma unroll
       for (int j = 0; j < TAPS; j++) {
-        v[j][0] = bf16lo_to_f32(vraw[j].x); v[j][1] = bf16hi_to_f32(vraw[j].x);
-        v[j][2] = bf16lo_to_f32(vraw[j].y); v[j][3] = bf16hi_to_f32(vraw[j].y);
+        v2[j][0] = pack_f32x2(bf16lo_to_f32(vraw[j].x), bf16hi_to_f32(vraw[j].x));
+        v2[j][1] = pack_f32x2(bf16lo_to_f32(vraw[j].y), bf16hi_to_f32(vraw[j].y));
       }
       __nv_bfloat16* obase = p.out + (size_t)t * TAPS * p.ldo + (size_t)h * 128 + 4 * lane;
 #pragma unroll
       for (int i = 0; i < TAPS; i++) {
-        float o[4] = {0.f, 0.f, 0.f, 0.f};
+        uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+        const ulonglong2* prow = (const ulonglong2*)&probs[warp][i][0];
 #pragma unroll
-        for (int j = 0; j < TAPS; j++) {
-          const float pij = probs[warp][i][j];
-#pragma unroll
-          for (int e = 0; e < 4; e++) o[e] = fmaf(pij, v[j][e], o[e]);
+        for (int jj = 0; jj < TAPS / 2; jj++) {         // taps in order, as the scalar sum would take them
+          const ulonglong2 pp = prow[jj];               // (p_2jj, p_2jj), (p_2jj+1, p_2jj+1)
+          acc0 = fma_f32x2(pp.x, v2[2 * jj][0], acc0);
+          acc1 = fma_f32x2(pp.x, v2[2 * jj][1], acc1);
+          acc0 = fma_f32x2(pp.y, v2[2 * jj + 1][0], acc0);
+          acc1 = fma_f32x2(pp.y, v2[2 * jj + 1][1], acc1);
         }
+        float o[4];
+        unpack_f32x2(acc0, o[0], o[1]);
+        unpack_f32x2(acc1, o[2], o[3]);
         const float g4[4] = {bf16lo_to_f32(gate[i].x), bf16hi_to_f32(gate[i].x), bf16lo_to_f32(gate[i].y), bf16hi_to_f32(gate[i].y)};
 #pragma unroll
         for (int e = 0; e < 4; e++) o[e] *= 1.0f / (1.0f + __expf(-g4[e]));   // common.h:24

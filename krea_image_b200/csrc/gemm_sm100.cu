@@ -243,7 +243,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
               for (int e = 0; e < 8; e++) {
                 const float gv = __uint_as_float(g[q4 * 8 + e]);
-                f[e] = gv / (1.0f + __expf(-gv)) * __uint_as_float(u[q4 * 8 + e]);      // common.h silu
+                f[e] = gv * sigmoid_approx(gv) * __uint_as_float(u[q4 * 8 + e]);      // common.h silu
               }
               *(uint4*)(crow + ocol0 + q4 * 8) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
             }

@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(LW_WARPS * 32) layerwise_attn_kernel(const Lay
         float l = (e0 + e1) + (e2 + e3);
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const float inv = 1.0f / l;
+        const float inv = rcp_approx(l);
         const int row = g + 8 * half;
         if (row < TAPS) {
           float4* prow = (float4*)&probs[warp][row][0];
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(LW_WARPS * 32) layerwise_attn_kernel(const Lay
         unpack_f32x2(acc1, o[2], o[3]);
         const float g4[4] = {bf16lo_to_f32(gate[i].x), bf16hi_to_f32(gate[i].x), bf16lo_to_f32(gate[i].y), bf16hi_to_f32(gate[i].y)};
 #pragma unroll
-        for (int e = 0; e < 4; e++) o[e] *= 1.0f / (1.0f + __expf(-g4[e]));   // common.h:24
+        for (int e = 0; e < 4; e++) o[e] *= sigmoid_approx(g4[e]);
         *(uint2*)(obase + (size_t)i * p.ldo) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
       }
     }

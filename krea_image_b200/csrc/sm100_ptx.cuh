@@ -293,6 +293,17 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 1 / x on the special-function unit (1 ulp).  A plain `1.0f / x` compiles to the IEEE sequence: the same unit, then
+// four corrections and a checked branch - ten instructions where the bf16 result needs one.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// sigmoid (engine/kernels/common.h:24) as one exp2, one add and one reciprocal
+__device__ __forceinline__ float sigmoid_approx(float x) {
+  return rcp_approx(1.0f + ex2_approx(-1.4426950408889634f * x));
+}
 // two fp32 -> packed bf16x2 (lo in the low half), round to nearest even
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;

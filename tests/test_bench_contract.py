@@ -4,6 +4,8 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -22,8 +24,9 @@ def test_reference_arm_prints_one_contract_line():
     assert d["config"]["workload"] == "c1-1024sq"
 
 
-def test_reference_arm_of_the_block_workload_says_unavailable():
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", "block"], capture_output=True, text=True, timeout=120)
+@pytest.mark.parametrize("workload", ["block", "gemm", "layerwise"])
+def test_reference_arm_of_the_adjacent_workloads_says_unavailable(workload):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", workload], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0
     d = json.loads(r.stdout.strip().splitlines()[-1])
     assert d["impl"] == "reference" and "unavailable" in d

@@ -264,6 +264,44 @@ def test_attention_gate(kc):
     check(host_f32(o), want, None, "gated attention")
 
 
+def test_gate_extremes_saturate_cleanly(kc):
+    """The sigmoid gate runs on the approximate exp2 and reciprocal of the special-function unit: gates far outside
+    the usual range (and +-inf, which bf16 can hold) must give exactly 0 or the ungated value, never NaN."""
+    rng = np.random.default_rng(43)
+    Lq, Lk, H = 140, 130, 2
+    ld = H * 128
+    Q, K, V = (synth.f32_to_bf16_bits(rng.standard_normal((n, ld)).astype(np.float32)) for n in (Lq, Lk, Lk))
+    gvals = np.array([-np.inf, -200.0, -90.0, -20.0, -1.0, 0.0, 1.0, 20.0, 90.0, 200.0, np.inf], dtype=np.float32)
+    G = synth.f32_to_bf16_bits(gvals[rng.integers(0, len(gvals), (Lq, ld))])
+    want = oracle.attention(Q, K, V, Lq, Lk, H, ld, ld, ld, G=G, ldg=ld)
+    o = torch.zeros((Lq, ld), dtype=torch.bfloat16, device="cuda")
+    kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), o, Lq, Lk, H, ld, ld, ld, ld, 1, False, 0, dev_bits(G), ld)
+    kc.wait()
+    got = host_f32(o)
+    check(got, want, None, "attention with extreme gates")
+    gf = synth.bf16_bits_to_f32(G)
+    assert np.all(got[gf <= -90.0] == 0.0)
+    plain = torch.zeros_like(o)
+    kc.attention(dev_bits(Q), dev_bits(K), dev_bits(V), plain, Lq, Lk, H, ld, ld, ld, ld, 1, False, 0, None, 0)
+    kc.wait()
+    assert np.array_equal(got[gf >= 20.0], host_f32(plain)[gf >= 20.0])     # sigmoid(20) rounds to 1 in fp32 already
+
+    # the layerwise kernel's gate: same values in the gate block of the fused rows
+    T, Hl = 9, 3
+    rows, ldl = T * 12, 4 * Hl * 128
+    x = (1.5 * rng.standard_normal((rows, ldl))).astype(np.float32)
+    x[:, 3 * Hl * 128:] = gvals[rng.integers(0, len(gvals), (rows, Hl * 128))]
+    xb = synth.f32_to_bf16_bits(x)
+    offs = (0, Hl * 128, 2 * Hl * 128, 3 * Hl * 128)
+    want = oracle.layerwise_attn(xb, rows, ldl, Hl, *offs)
+    ol = torch.full((rows, Hl * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc.layerwise_attn(dev_bits(xb), ol, rows, ldl, Hl * 128, Hl, *offs)
+    kc.wait()
+    gotl = host_f32(ol)
+    check(gotl, want, None, "layerwise attention with extreme gates")
+    assert np.all(gotl[x[:, 3 * Hl * 128:] <= -90.0] == 0.0)
+
+
 def test_attention_large_logits_lazy_max(kc):
     """Scores that keep growing along the key axis force repeated running-max updates and O rescales."""
     rng = np.random.default_rng(43)

@@ -38,6 +38,7 @@ struct Json {
   const char* p;
   const char* end;
   std::string err;
+  int depth = 0;            // nesting of the value being skipped: a header is a few levels deep, never hundreds
 
   void ws() {
     while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++;
@@ -91,6 +92,15 @@ struct Json {
     if (out) *out = v;
     return true;
   }
+  // a size, offset or dimension: a whole number that a double holds exactly (strtod also accepts "inf", "nan"
+  // and values far beyond any file, and converting those to an integer is undefined)
+  bool count(uint64_t* out) {
+    double v = 0;
+    if (!number(&v)) return false;
+    if (!(v >= 0.0 && v <= 9007199254740992.0) || v != floor(v)) return fail("expected a non-negative whole number");
+    *out = (uint64_t)v;
+    return true;
+  }
   // skips any value; used for members this reader does not interpret
   bool skip() {
     ws();
@@ -101,10 +111,12 @@ struct Json {
       const bool obj = *p == '{';
       p++;
       if (lit(close)) return true;
+      if (++depth > 64) return fail("header nested too deeply");
       do {
         if (obj && (!string(nullptr) || !lit(':'))) return fail("bad object member");
         if (!skip()) return false;
       } while (lit(','));
+      depth--;
       return lit(close) ? true : fail("unterminated container");
     }
     if (!strncmp(p, "true", 4)) { p += 4; return true; }
@@ -120,24 +132,24 @@ bool parse_tensor(Json& j, QwTensor* t) {
   do {
     std::string key;
     if (!j.string(&key) || !j.lit(':')) return j.fail("bad tensor member");
-    double v = 0;
+    uint64_t v = 0;
     if (key == "dtype") {
       if (!j.string(&t->dtype)) return false;
     } else if (key == "shape") {
       if (!j.lit('[')) return j.fail("shape is not an array");
       if (!j.lit(']')) {
         do {
-          if (!j.number(&v)) return false;
+          if (!j.count(&v)) return false;
           t->shape.push_back((int64_t)v);
         } while (j.lit(','));
         if (!j.lit(']')) return j.fail("unterminated shape");
       }
     } else if (key == "offset") {
-      if (!j.number(&v)) return false;
-      t->offset = (uint64_t)v;
+      if (!j.count(&v)) return false;
+      t->offset = v;
     } else if (key == "nbytes") {
-      if (!j.number(&v)) return false;
-      t->nbytes = (uint64_t)v;
+      if (!j.count(&v)) return false;
+      t->nbytes = v;
     } else if (!j.skip()) {
       return false;
     }
@@ -245,7 +257,7 @@ krea_qw* krea_cuda_qw_open(const char* path, char* err, int errlen) {
     uint64_t n = dtype_size(t.dtype);
     if (n == 0) return bail("tensor " + t.name + ": unknown dtype " + t.dtype);
     for (int64_t d : t.shape) {
-      if (d < 0) return bail("tensor " + t.name + ": negative dimension");
+      if (d != 0 && n > UINT64_MAX / (uint64_t)d) return bail("tensor " + t.name + ": shape overflows");
       n *= (uint64_t)d;
     }
     if (n != t.nbytes) return bail("tensor " + t.name + ": shape and nbytes disagree");

@@ -75,6 +75,29 @@ def test_reader_rejects_damaged_files(tmp_path):
     hdr["tensors"]["L0.qn"]["shape"] = [127]
     hj = json.dumps(hdr).encode().ljust(hlen)                           # same length: offsets stay valid
     expect("shape.qw", raw[:16] + hj + raw[16 + hlen:], "disagree")
+
+    # numbers that are no sizes: negative, fractional, infinite, beyond any file; a shape whose product wraps around
+    # 64 bits; a header nested deeper than any converter writes
+    def with_header(mutate):
+        h = json.loads(raw[16:16 + hlen])
+        mutate(h)
+        hj = json.dumps(h).encode()
+        assert len(hj) <= hlen + ALIGN - 64
+        body = b"QWTS" + struct.pack("<IQ", 1, len(hj)) + hj
+        start = (len(body) + ALIGN - 1) // ALIGN * ALIGN
+        old_start = (16 + hlen + ALIGN - 1) // ALIGN * ALIGN
+        return body.ljust(start, b"\0") + raw[old_start:]
+
+    def set_field(field, value):
+        return lambda h: h["tensors"]["L0.qn"].__setitem__(field, value)
+
+    expect("neg.qw", with_header(set_field("offset", -16384)), "whole number")
+    expect("frac.qw", with_header(set_field("nbytes", 511.5)), "whole number")
+    expect("huge.qw", with_header(set_field("offset", 1e300)), "whole number")
+    expect("inf.qw", with_header(set_field("offset", 0)).replace(b'"offset": 0', b'"offset": inf', 1), "header")
+    expect("wrap.qw", with_header(set_field("shape", [2 ** 32, 2 ** 32, 128])), "overflows")
+    deep = json.loads("[" * 100 + "]" * 100)
+    expect("deep.qw", with_header(lambda h: h.__setitem__("extra", deep)), "nested")
     with pytest.raises(KreaCudaError):
         weights.WeightFile(tmp_path / "absent.qw")
 

@@ -328,11 +328,12 @@ int krea_cuda_qw_upload(krea_cuda* h, const krea_qw* q, uint64_t off, uint64_t l
     }
   }
   cudaEvent_t done[2] = {nullptr, nullptr};
-  for (int i = 0; i < 2; i++) CUDA_TRY(h, cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+  cudaError_t e = cudaSuccess;
+  for (int i = 0; i < 2 && e == cudaSuccess; i++) e = cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming);
   const char* src = (const char*)krea_cuda_qw_host_ptr(q, off);
   int rc = KREA_CUDA_OK;
   // (every upload ends with a stream synchronisation, so both halves are free here)
-  cudaError_t e = cudaStreamSynchronize(h->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);
   int k = 0;
   for (uint64_t o = 0; o < len && e == cudaSuccess; o += chunk, k ^= 1) {
     const size_t n = (size_t)std::min<uint64_t>(chunk, len - o);
@@ -345,7 +346,8 @@ int krea_cuda_qw_upload(krea_cuda* h, const krea_qw* q, uint64_t off, uint64_t l
   }
   if (e == cudaSuccess) e = cudaStreamSynchronize(h->stream);   // the halves are free again on return
   if (e != cudaSuccess) rc = fail(h, KREA_CUDA_E_CUDA, "qw_upload: %s", cudaGetErrorString(e));
-  for (int i = 0; i < 2; i++) cudaEventDestroy(done[i]);
+  for (int i = 0; i < 2; i++)
+    if (done[i]) cudaEventDestroy(done[i]);
   return rc;
 }
 

@@ -391,8 +391,8 @@ KREA_CUDA_API int krea_cuda_reshard_unpack(krea_cuda* h, const krea_cuda_reshard
  * single-GPU entry points.  Rank 0 obtains an id with krea_cuda_dist_unique_id and hands the 128 bytes to
  * every rank by whatever means the host program has (a file, a socket, MPI, torch.distributed);
  * krea_cuda_dist_init is collective over the nranks handles.  Everything is enqueued on the handle's
- * stream; remote rows are always landed in local memory by NCCL before a kernel of this library reads
- * them.
+ * stream; remote rows always land in local memory (through NCCL, or through the sending rank's own stores in
+ * peer-store mode) before a kernel of this library reads them.
  *
  * Layout: with S rows and H heads over P ranks (S and H multiples of P), rank r starts with rows
  * [r*S/P, (r+1)*S/P) of every head ("sequence-sharded") and the exchange gives it every row of heads

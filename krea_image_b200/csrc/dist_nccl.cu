@@ -4,8 +4,10 @@
 // what is kept from it is that heads are independent units of work (grid.y = heads, metal.mm:199-201).
 //
 // NCCL is loaded at run time, so the library has no link-time dependency on it and the single-GPU entry
-// points work on a machine without NCCL.  Remote rows are landed in local memory by ncclSend/ncclRecv;
-// no kernel of this library dereferences a peer's memory.
+// points work on a machine without NCCL.  Remote rows always land in local memory before a kernel reads
+// them: by ncclSend/ncclRecv, or - in peer-store mode - by the sending rank's own kernels, which write the
+// destination GPU's mapped workspace with plain 16-byte stores.  No kernel of this library ever reads a
+// peer's memory, and no TMA operation touches it.
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdlib.h>

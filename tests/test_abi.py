@@ -51,6 +51,37 @@ def test_struct_layouts_match_header_field_order():
         assert fields == [f[0] for f in st._fields_], cname
 
 
+_STRUCTS = (("krea_cuda_qknorm_args", "QKNormArgs"), ("krea_cuda_attn_args", "AttnArgs"), ("krea_cuda_joint_args", "JointArgs"),
+            ("krea_cuda_reshard_args", "ReshardArgs"), ("krea_cuda_layerwise_args", "LayerwiseArgs"), ("krea_cuda_gemm_args", "GemmArgs"),
+            ("krea_cuda_rmsnorm_args", "RmsNormArgs"), ("krea_cuda_dequant_args", "DequantArgs"), ("krea_cuda_dit_block_args", "DitBlockArgs"),
+            ("krea_cuda_a2a_args", "A2AArgs"), ("krea_cuda_seqpar_args", "SeqParArgs"), ("krea_cuda_qw_info", "QwInfo"))
+
+
+def test_struct_sizes_and_field_offsets_match_the_c_compiler(tmp_path):
+    """Field names in the right order are not enough: a ctypes field one type too narrow shifts everything after it.
+    A C program built from the header prints sizeof and every offsetof; the ctypes mirrors must agree byte for byte."""
+    import ctypes
+    import subprocess
+    lines = ["#include <stddef.h>", "#include <stdio.h>", '#include "krea_cuda.h"', "int main(void) {"]
+    for cname, pyname in _STRUCTS:
+        st = getattr(binding, pyname)
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for field in st._fields_:
+            lines.append(f'  printf("{cname}.{field[0]} %zu\\n", offsetof({cname}, {field[0]}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines) + "\n")
+    exe = tmp_path / "layout"
+    r = subprocess.run(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    got = dict(line.split() for line in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.splitlines())
+    for cname, pyname in _STRUCTS:
+        st = getattr(binding, pyname)
+        assert int(got[cname]) == ctypes.sizeof(st), cname
+        for field in st._fields_:
+            assert int(got[f"{cname}.{field[0]}"]) == getattr(st, field[0]).offset, f"{cname}.{field[0]}"
+
+
 def test_rope_tables_match_oracle():
     for T, gh, gw in ((512, 32, 32), (7, 3, 5), (0, 2, 2), (4, 0, 0)):
         c, s = ops.rope_tables_axial2d(T, gh, gw)

@@ -17,9 +17,17 @@ roofline the attention kernel alone (CUDA events around each launch) against the
 cpu_baseline  the CPU oracle (fp32) on this machine's cores, rank 0 at N=1 only
 --impl reference  times that CPU implementation instead (the reference has no other runnable code
          for this path off macOS)
---workload c4 is the long-sequence configuration (sequence-parallel over the GPUs); block, gemm and
-         layerwise time the kernels either side of the attention (a whole DiT block, its q|k|v|gate
-         projection, the text fusion's 12-tap attention), each with its own metric and roofline.
+multi    measured in the same process at every N (the two ways the path shards over GPUs):
+         head_split_c3  the 2048^2 configuration (S=16896) with the 24 heads split over the GPUs, no
+                        data-path collective (strong scaling);
+         seqpar_c4      the long-sequence configuration (S=66048): rows start sequence-sharded, are
+                        resharded to heads over NVLink, attended to, and the output rows brought home
+                        (strong scaling; at N=1 the fused call alone);
+         each with its time per step (max over ranks) and a parity check of the rows of the committed
+         golden fixtures that each rank owns, reduced over the ranks.
+--workload c4 is the long-sequence configuration alone; block, gemm and layerwise time the kernels
+         either side of the attention (a whole DiT block, its q|k|v|gate projection, the text fusion's
+         12-tap attention), each with its own metric and roofline.
 """
 import argparse
 import json
@@ -39,9 +47,11 @@ from krea_image_b200 import synth  # noqa: E402
 METRIC = "joint-attn TFLOP/s at S=4608 (1024^2), 24 heads, head_dim 128"
 FALLBACK_PEAK_TFLOPS = 1590.0
 WORKLOADS = {"c0": 0, "c1": 1, "c2": 2, "c3": 3, "c4": 4}
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at config 1, from the ncu capture
-# summarised under profiles/: 87.5 MB read + 8.8 MB written (algorithmic 113.2 MB; the output stays in L2)
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at config 1, from one ncu capture of
+# this workload: 87.5 MB read + 8.8 MB written (algorithmic 113.2 MB; the output stays in L2)
 ATTN_DRAM_TRAFFIC_BYTES = {1: 96.3e6}
+REPEATS = 9          # timed batches of `steps` steps each; the reported time per step is the median batch
+PARITY_REL_L2, PARITY_MAX_ABS = 5e-3, 2e-2
 
 
 def measured_peaks():
@@ -124,9 +134,23 @@ def cpu_oracle_sample(cfg, heads_sel, repeats=1):
     return flops / best / 1e12, best, oracle.num_threads()
 
 
+def attention_config(cfg, world, by_heads):
+    """The `config` object of a joint-attention line.  Both arms print the same one: it names the workload, not
+    the machine that runs it."""
+    Hl = cfg.heads // world if by_heads else cfg.heads
+    per_step = synth.attention_flops(cfg, synth.text_lengths(cfg) if cfg.masked else None)
+    set_bytes = cfg.batch * cfg.seq * cfg.heads * 128 * 2 * 4
+    nsets = max(2, int(np.ceil(3 * 126e6 / set_bytes)))
+    return {"workload": cfg.name, "batch": cfg.batch, "heads": cfg.heads, "seq": cfg.seq, "head_dim": 128,
+            "per_gpu": f"{Hl} of {cfg.heads} heads of one problem, no collective" if by_heads else "one full problem (all heads)",
+            "l2": f"on the GPU the steps rotate over {nsets} input/output sets ({nsets * set_bytes / 1e6:.0f} MB > 126 MB L2)",
+            "flops_per_step_per_gpu": per_step / world if by_heads else per_step}
+
+
 def run_reference(args, rank, world):
     """The reference arm: the only runnable statement of the reference's math here is the CPU oracle (the
-    reference itself is Metal-only), timed with every host thread on a bounded sample per step."""
+    reference itself is Metal-only), timed with every host thread.  One step = the whole workload (all heads)
+    for the configurations a CPU finishes in about a second; a stated sample of heads for the larger ones."""
     if rank != 0:
         return
     if args.workload in ("block", "gemm", "layerwise"):
@@ -135,129 +159,275 @@ def run_reference(args, rank, world):
     import oracle
     oracle.set_num_threads(os.cpu_count() or 1)       # torchrun exports OMP_NUM_THREADS=1; this arm runs on one rank only
     cfg = synth.CONFIGS[WORKLOADS[args.workload]]
-    heads_sel = list(range(0, cfg.heads, 6))          # 4 of 24 heads per step
-    qkv = synth.qkv_slice(cfg, nb=1)
+    if cfg.cid <= 1:
+        heads_sel = list(range(cfg.heads))
+        qkv = synth.qkv_slice(cfg, nb=1)
+        H = cfg.heads
+    else:                                             # a bounded sample: 2 heads of sample 0 (c2, c3), 1 head of c4
+        heads_sel = [0, cfg.heads // 2] if cfg.cid < 4 else [0]
+        qkv = np.concatenate([synth.qkv_slice(cfg, head0=h, nheads=1, nb=1).reshape(cfg.seq, 3, 128) for h in heads_sel], axis=2)
+        qkv = np.ascontiguousarray(qkv).reshape(1, cfg.seq, 3 * len(heads_sel) * 128)
+        H = len(heads_sel)
+        heads_sel = list(range(H))
     wq, wk = synth.qk_weights(cfg)
     cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
     flops = 4.0 * 128 * len(heads_sel) * float(cfg.seq) ** 2
     for _ in range(args.warmup):
-        oracle.joint_attention(qkv, 1, cfg.seq, cfg.heads, wq, wk, cos, sin, heads_sel=heads_sel)
+        oracle.joint_attention(qkv, 1, cfg.seq, H, wq, wk, cos, sin, heads_sel=heads_sel)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.joint_attention(qkv, 1, cfg.seq, cfg.heads, wq, wk, cos, sin, heads_sel=heads_sel)
+        oracle.joint_attention(qkv, 1, cfg.seq, H, wq, wk, cos, sin, heads_sel=heads_sel)
     dt = (time.perf_counter() - t0) / args.steps
     val = flops / dt / 1e12
-    sample = f"{len(heads_sel)} of {cfg.heads} heads of {cfg.name} per step (S={cfg.seq}), fp32 oracle, OpenMP"
-    print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+    sample = f"{len(heads_sel)} of {cfg.heads} heads of {cfg.name}, sample 0, per step (S={cfg.seq}), fp32 oracle, OpenMP"
+    line = {
+        "impl": "reference", "metric": METRIC if cfg.cid == 1 else f"joint-attn TFLOP/s at S={cfg.seq}, B={cfg.batch}, 24 heads, head_dim 128",
+        "value": val, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg.name, "batch": cfg.batch, "heads": cfg.heads, "seq": cfg.seq, "head_dim": 128},
+        "config": attention_config(cfg, world, False),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference's own implementation of this path is Metal-only (unavailable on this box); "
                 "this arm times the CPU restatement of its math",
-    }))
+    }
+    if world > 1:
+        line["note"] += "; reference arm is single-process: rank 0 alone runs it, its value does not grow with n_gpus"
+    print(json.dumps(line))
 
 
-def run_seq_parallel(args, rank, world, local_rank):
-    """--workload c4: the long-sequence configuration, strong scaling.  Rows start sequence-sharded over the
-    ranks; every step reshards Q, K, V to heads with an all-to-all, runs the fused call on full sequences
-    and brings the output rows back (at N=1 there is nothing to exchange: the fused call alone)."""
+class Ranks:
+    """The little this benchmark needs from torch.distributed: barriers around timed regions and reductions
+    of a few numbers.  With one process everything is the identity."""
+
+    def __init__(self, rank, world):
+        self.rank, self.world = rank, world
+
+    def barrier(self):
+        import torch
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def reduce(self, values, op="max"):
+        """Element-wise max / min / sum over the ranks of a list of floats."""
+        if self.world == 1:
+            return [float(v) for v in values]
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor(list(values), dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "sum": dist.ReduceOp.SUM}[op])
+        return [float(v) for v in t.tolist()]
+
+
+def timed_batches(step, steps, repeats, stream, ranks):
+    """`repeats` timed batches of exactly `steps` calls of step(i), each bracketed by a barrier and a device
+    synchronisation on both sides and timed with CUDA events on the launching stream.  Returns the time per
+    step of every batch, max over ranks."""
     import torch
-    import torch.distributed as dist
+    out, k = [], 0
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ranks.barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            step(k)
+            k += 1
+        e1.record(stream)
+        ranks.barrier()
+        out.append(e0.elapsed_time(e1) / steps)
+    return ranks.reduce(out, "max")
+
+
+def spread(ms_list):
+    return {"ms_per_step": float(np.median(ms_list)), "ms_min": float(min(ms_list)), "ms_max": float(max(ms_list)), "batches": len(ms_list)}
+
+
+class GoldenRows:
+    """Sampled output rows of one configuration from the committed fixtures (fp32 values of the CPU oracle,
+    written by tests/golden/make_golden.py): block i holds rows[i] of head head[i] of sample 0."""
+
+    def __init__(self, cid):
+        d = np.load(os.path.join(ROOT, "tests", "golden", f"c{cid}_rows.npz"))
+        self.head, self.rows, self.want = d["head_of_block"], d["rows"], d["fp32"]
+
+    def check(self, out, row_lo, row_hi, head_lo, head_hi, ranks):
+        """out: bf16 device tensor [row_hi - row_lo, (head_hi - head_lo) * 128] = this rank's rows and heads of
+        the output.  Compares the fixture rows that lie inside with the fixture, reduces over the ranks."""
+        import torch
+        d2 = w2 = mx = 0.0
+        n = 0
+        for i, h in enumerate(self.head):
+            if not head_lo <= h < head_hi:
+                continue
+            sel = np.nonzero((self.rows[i] >= row_lo) & (self.rows[i] < row_hi))[0]
+            if len(sel) == 0:
+                continue
+            idx = torch.from_numpy((self.rows[i][sel] - row_lo).astype(np.int64)).to(out.device)
+            got = out[idx, (h - head_lo) * 128:(h - head_lo + 1) * 128].float().cpu().numpy()
+            diff = got.astype(np.float64) - self.want[i][sel]
+            d2 += float((diff * diff).sum())
+            w2 += float((self.want[i][sel].astype(np.float64) ** 2).sum())
+            mx = max(mx, float(np.abs(diff).max()))
+            n += len(sel)
+        d2, w2, n = ranks.reduce([d2, w2, n], "sum")
+        mx, = ranks.reduce([mx], "max")
+        rel = float(np.sqrt(d2 / w2)) if w2 > 0 else None
+        return {"rel_l2": rel, "max_abs": mx, "rows": int(n), "rows_in_fixture": int(self.rows.size),
+                "against": "fp32 CPU oracle rows committed under tests/golden", "tolerance": {"rel_l2": PARITY_REL_L2, "max_abs": PARITY_MAX_ABS},
+                "ok": bool(rel is not None and rel <= PARITY_REL_L2 and mx <= PARITY_MAX_ABS and n == self.rows.size)}
+
+
+def measure_head_split(kc, cid, steps, warmup, repeats, ranks, stream):
+    """One problem of configuration `cid`, its heads split evenly over the ranks; every rank runs the fused
+    call on its heads.  Heads are independent (the reference runs one threadgroup column per head,
+    engine/src/metal.mm:199-201), so nothing is exchanged."""
+    import torch
+    cfg = synth.CONFIGS[cid]
+    S, H, world, rank = cfg.seq, cfg.heads, ranks.world, ranks.rank
+    if H % world:
+        return {"skipped": f"{H} heads do not split over {world} GPUs"}
+    Hl = H // world
+    h0 = rank * Hl
+    ld = 3 * Hl * 128
+    qkv = torch.from_numpy(synth.qkv_slice(cfg, head0=h0, nheads=Hl)[0].view(np.int16))
+    set_bytes = S * Hl * 128 * 2 * 4
+    nsets = max(2, int(np.ceil(3 * 126e6 / set_bytes)))          # one pass never finds its operands in L2
+    xs = [qkv.cuda().view(torch.bfloat16).view(-1) for _ in range(nsets)]
+    os_ = [torch.zeros((S, Hl * 128), dtype=torch.bfloat16, device="cuda") for _ in range(nsets)]
+    wq, wk = synth.qk_weights(cfg)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_wq, d_wk, d_cos, d_sin = dev(wq), dev(wk), dev(cos), dev(sin)
+
+    def step(i):
+        x, o = xs[i % nsets], os_[i % nsets]
+        kc.joint_attention(x, x[Hl * 128:], x[2 * Hl * 128:], o, S, S, Hl, ld, ld, ld, Hl * 128, d_wq, d_wk, d_cos, d_sin)
+
+    for i in range(warmup):
+        step(i)
+    kc.wait()
+    ms = timed_batches(step, steps, repeats, stream, ranks)
+    kc.wait()
+    parity = GoldenRows(cid).check(os_[(repeats * steps - 1) % nsets], 0, S, h0, h0 + Hl, ranks)
+    res = spread(ms)
+    res.update({"workload": cfg.name, "seq": S, "heads_per_gpu": Hl, "scaling": "strong", "collective": None, "steps": steps,
+                "tflops": synth.attention_flops(cfg) / (res["ms_per_step"] * 1e-3) / 1e12,
+                "l2": f"rotating {nsets} input/output sets ({nsets * set_bytes / 1e6:.0f} MB per GPU > 126 MB L2)", "parity": parity})
+    return res
+
+
+def measure_seq_parallel(kc, steps, warmup, repeats, ranks, stream, a2a="native"):
+    """Configuration 4 (S = 66048): rows start sequence-sharded over the ranks; every step reshards Q, K, V to
+    heads, runs the fused call on full sequences and brings the output rows home (at one rank there is nothing
+    to exchange: the fused call alone).  Returns timings (max over ranks), the phase timers of rank 0 and the
+    parity of the fixture rows every rank owns."""
+    import torch
 
     from krea_image_b200 import dist as kd
-    from krea_image_b200 import ops
 
-    torch.cuda.set_device(local_rank)
     cfg = synth.CONFIGS[4]
-    S, H = cfg.seq, cfg.heads
+    S, H, world, rank = cfg.seq, cfg.heads, ranks.world, ranks.rank
+    if S % world or H % world:
+        return {"skipped": f"S={S}, {H} heads do not split over {world} GPUs"}
     ld = 3 * H * 128
-    kc = ops.KreaCuda(local_rank)
-    stream = torch.cuda.current_stream()
-    kc.set_stream(stream)
     plan = kd.UlyssesPlan(S, H, world)
     lo, hi = plan.row_range(rank)
     x = torch.from_numpy(synth.qkv_slice(cfg, row0=lo, nrows=hi - lo)[0].view(np.int16)).cuda().view(torch.bfloat16)
     wq, wk = synth.qk_weights(cfg)
-    cos, sin = ops.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
+    cos, sin = synth.rope_tables_axial2d(cfg.text, cfg.grid, cfg.grid)
     dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
     d_wq, d_wk, d_cos, d_sin = dev(wq), dev(wk), dev(cos), dev(sin)
-    flops = synth.attention_flops(cfg)
-    if world > 1 and args.a2a == "native":
+    out = torch.zeros((hi - lo, H * 128), dtype=torch.bfloat16, device="cuda")
+    exchange = None
+    if world > 1 and a2a == "native":
         kd.init_native(kc)                     # the library's own NCCL communicator: one C call per step
+        mode = kc.dist_exchange_mode()
         exchange = {"p2p": "peer stores over NVLink inside libkrea_cuda (pack kernels and attention epilogue), NCCL barriers",
-                    "nccl": "ncclSend/ncclRecv inside libkrea_cuda"}[kc.dist_exchange_mode()]
+                    "nccl": "ncclSend/ncclRecv inside libkrea_cuda"}[mode]
         ua = kd.NativeUlyssesAttention(kc, plan)
-        step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
+        step = lambda i: ua(x, d_wq, d_wk, d_cos, d_sin, out=out)
     elif world > 1:
+        mode, exchange = "torch", "torch.distributed all_to_all_single"
         ua = kd.UlyssesAttention(kc, plan, kd.TorchGroup())
-        step = lambda: ua(x, d_wq, d_wk, d_cos, d_sin)
+
+        def step(i):
+            out.copy_(ua(x, d_wq, d_wk, d_cos, d_sin))
     else:
-        o = torch.empty((S, H * 128), dtype=torch.bfloat16, device="cuda")
+        mode = "none"
         xf = x.view(-1)
-        step = lambda: kc.joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o, S, S, H, ld, ld, ld, H * 128, d_wq, d_wk, d_cos, d_sin)
+        step = lambda i: kc.joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], out, S, S, H, ld, ld, ld, H * 128, d_wq, d_wk, d_cos, d_sin)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
+    for i in range(warmup):
+        step(i)
     kc.wait()
+    n0 = kc.launches
+    ms = timed_batches(step, steps, repeats, stream, ranks)
+    launches = (kc.launches - n0) // repeats
+    kc.wait()
+    parity = GoldenRows(4).check(out, lo, hi, 0, H, ranks)
+    # phase timers (CUDA events around the library's own launches) on a few more steps
+    nprof = min(steps, 5)
+    kc.profile(True)
+    for i in range(nprof):
+        step(i)
+    attn_ms, attn_n = kc.profile_read(1)
+    norm_ms, norm_n = kc.profile_read(0)
+    xchg_ms, _ = kc.profile_read(2)
+    bar_ms, _ = kc.profile_read(3)
+    kc.profile(False)
+    ranks.barrier()
+    if world > 1 and a2a == "native":
+        kc.dist_shutdown()
+    res = spread(ms)
+    flops = synth.attention_flops(cfg)
+    res.update({"workload": cfg.name, "seq": S, "heads_per_gpu": H // world, "rows_per_gpu": hi - lo, "scaling": "strong",
+                "exchange": mode, "exchange_detail": exchange, "steps": steps, "launches_per_batch": int(launches),
+                "tflops": flops / (res["ms_per_step"] * 1e-3) / 1e12,
+                "attn_ms": attn_ms / max(attn_n, 1), "prepass_ms": norm_ms / max(norm_n, 1), "exchange_ms": xchg_ms / nprof,
+                "barrier_ms": bar_ms / nprof, "phase_timers": "rank 0, CUDA events around each launch inside the library",
+                "l2": "inputs (1.2 GB over all GPUs, 152 MB per GPU at 8) exceed the 126 MB L2", "parity": parity})
+    return res
+
+
+def run_seq_parallel(args, rank, world, local_rank):
+    """--workload c4: the long-sequence configuration alone, strong scaling."""
+    import torch
+
+    from krea_image_b200 import ops
+
+    torch.cuda.set_device(local_rank)
+    cfg = synth.CONFIGS[4]
+    kc = ops.KreaCuda(local_rank)
+    stream = torch.cuda.current_stream()
+    kc.set_stream(stream)
+    ranks = Ranks(rank, world)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    barrier()
-    n0 = kc.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
-    launches = kc.launches - n0
-    kc.wait()
-    ms = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    m = measure_seq_parallel(kc, args.steps, max(args.warmup, 3), 3, ranks, stream, args.a2a)
     clocks = sampler.stop() if rank == 0 else None
-    # the attention kernel alone (events around its launches), for the roofline of this rank's share
-    kc.profile(True)
-    for _ in range(min(args.steps, 5)):
-        step()
-    attn_ms, attn_n = kc.profile_read(1)
-    norm_ms, norm_n = kc.profile_read(0)
-    xchg_ms, xchg_n = kc.profile_read(2)
-    bar_ms, bar_n = kc.profile_read(3)
-    nprof = min(args.steps, 5)
-    kc.profile(False)
-    barrier()
     if rank == 0:
         peak, peak_sustained, peak_kind = measured_peaks()
-        value = flops / (ms * 1e-3) / 1e12
-        attn_ms_avg = attn_ms / max(attn_n, 1)
-        attn_tflops = flops / world / (attn_ms_avg * 1e-3) / 1e12
+        flops = synth.attention_flops(cfg)
+        attn_tflops = flops / world / (m["attn_ms"] * 1e-3) / 1e12
         roofline = {"bound": "tensor", "achieved": attn_tflops, "peak": peak_sustained, "unit": "TFLOP/s", "frac": attn_tflops / peak_sustained,
                     "traffic": None, "peak_kind": f"{peak_kind} sustained bf16 GEMM (kernels of several ms run under the power cap)",
-                    "kernel": "attn_fwd_sm100", "kernel_ms": attn_ms_avg, "launches_timed": attn_n,
-                    "prologue_kernel_ms": norm_ms / max(norm_n, 1), "exchange_kernels_ms_per_step": xchg_ms / nprof, "rank_barriers_ms_per_step": bar_ms / nprof,
-                    "step_minus_kernels_ms": ms - attn_ms_avg - norm_ms / max(norm_n, 1)}
+                    "kernel": "attn_fwd_sm100", "kernel_ms": m["attn_ms"], "prologue_kernel_ms": m["prepass_ms"],
+                    "exchange_kernels_ms_per_step": m["exchange_ms"], "rank_barriers_ms_per_step": m["barrier_ms"],
+                    "step_minus_kernels_ms": m["ms_per_step"] - m["attn_ms"] - m["prepass_ms"]}
         print(json.dumps({
-            "metric": "joint-attn TFLOP/s at S=66048 (4096^2), 24 heads, head_dim 128, sequence-parallel", "value": value,
-            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "metric": "joint-attn TFLOP/s at S=66048 (4096^2), 24 heads, head_dim 128, sequence-parallel", "value": m["tflops"],
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": m["ms_per_step"],
+            "ms_min": m["ms_min"], "ms_max": m["ms_max"], "timed_batches": m["batches"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "batch": 1, "heads": H, "seq": S, "head_dim": 128,
-                       "parallelism": f"sequence-sharded in/out, all-to-all to {H // world} heads per GPU" if world > 1 else "single GPU",
-                       "exchange": (exchange if args.a2a == "native" else "torch.distributed all_to_all_single") if world > 1 else None,
-                       "l2": "inputs (1.2 GB) exceed the 126 MB L2"},
-            "pct_of_measured_bf16_peak": 100.0 * value / world / peak, "gpu_launches": int(launches), "clocks": clocks,
-            "e2e": None, "roofline": roofline}))
+            "config": {"workload": cfg.name, "batch": 1, "heads": cfg.heads, "seq": cfg.seq, "head_dim": 128,
+                       "parallelism": f"sequence-sharded in/out, all-to-all to {cfg.heads // world} heads per GPU" if world > 1 else "single GPU",
+                       "exchange": m["exchange_detail"], "l2": m["l2"]},
+            "pct_of_measured_bf16_peak": 100.0 * m["tflops"] / world / peak, "gpu_launches": m["launches_per_batch"], "clocks": clocks,
+            "e2e": None, "roofline": roofline, "parity": m["parity"]}))
     kc.close()
 
 
@@ -419,7 +589,7 @@ def run_kernel_workload(args, rank, world, local_rank):
         metric = "layerwise (12-tap) attention GB/s, 4096 tokens x 20 heads, head_dim 128"
         config = {"workload": "layerwise-4096tok", "tokens": T, "taps": 12, "heads": H, "head_dim": 128,
                   "l2": "two rotating inputs (1007 MB each > 126 MB L2)", "bytes_per_step_per_gpu": work}
-        kernel, traffic = "layerwise_attn_kernel", 1241e6      # one ncu capture of this workload, summarised under profiles/
+        kernel, traffic = "layerwise_attn_kernel", 1241e6      # dram bytes of one launch, from one ncu capture of this workload
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -441,7 +611,6 @@ def run_kernel_workload(args, rank, world, local_rank):
 
 def run_ours(args, rank, world, local_rank):
     import torch
-    import torch.distributed as dist
 
     from krea_image_b200 import ops
 
@@ -458,6 +627,7 @@ def run_ours(args, rank, world, local_rank):
     kc = ops.KreaCuda(local_rank)          # no fallback: raises if the CUDA library cannot be loaded
     stream = torch.cuda.current_stream()
     kc.set_stream(stream)
+    ranks = Ranks(rank, world)
     # units of work: whole samples per GPU (weak scaling), or this rank's heads of the one problem (strong
     # scaling; heads are independent, so there is still no data-path collective)
     by_heads = args.shard == "heads" and world > 1
@@ -483,44 +653,29 @@ def run_ours(args, rank, world, local_rank):
     xs = [qkv_h.cuda().view(torch.bfloat16).view(-1) for _ in range(nsets)]
     os_ = [torch.empty((B, S, H * 128), dtype=torch.bfloat16, device="cuda") for _ in range(nsets)]
 
-    def step(i):
-        x, o = xs[i % nsets], os_[i % nsets]
-        kc.joint_attention(x[h0 * 128:], x[(H + h0) * 128:], x[(2 * H + h0) * 128:], o.view(-1)[h0 * 128:], S, S, Hl, ld, ld, ld, H * 128,
-                           d_wq, d_wk, d_cos, d_sin, 1e-6, 1, 0, 0,
-                           batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=d_tl, text_slots=cfg.text if tl is not None else 0)
+    def make_step(k):
+        def step(i):
+            x, o = xs[i % nsets], os_[i % nsets]
+            k.joint_attention(x[h0 * 128:], x[(H + h0) * 128:], x[(2 * H + h0) * 128:], o.view(-1)[h0 * 128:], S, S, Hl, ld, ld, ld, H * 128,
+                              d_wq, d_wk, d_cos, d_sin, 1e-6, 1, 0, 0,
+                              batch=B, bsq=S * ld, bsk=S * ld, bsv=S * ld, bso=S * H * 128, text_len=d_tl, text_slots=cfg.text if tl is not None else 0)
+        return step
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    for i in range(max(args.warmup, 3)):
+    step = make_step(kc)
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
         step(i)
     kc.wait()
 
-    # ---- device-resident timing ----
+    # ---- device-resident timing: REPEATS batches of exactly `steps` steps, the median batch is reported ----
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    barrier()
     n0 = kc.launches
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    barrier()
-    launches = kc.launches - n0
+    ms_batches = timed_batches(step, args.steps, REPEATS, stream, ranks)
+    launches = (kc.launches - n0) // REPEATS
     kc.wait()                                # also surfaces a device-side timeout as an error
-    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    ms_step = float(np.median(ms_batches))
     # keep the GPU busy a little longer so the clock sampler sees the loaded state
     t_end = time.perf_counter() + (0.6 if rank == 0 else 0.0)
     i = 0
@@ -541,6 +696,29 @@ def run_ours(args, rank, world, local_rank):
     kc.profile(False)
     attn_ms_avg = attn_ms / max(attn_n, 1)
 
+    # ---- which softmax form ran, and the other one beside it ----
+    # The fused call uses the bounded form when 128 * max|wq| * max|wk| / sqrt(128) * log2(e) <= 40 (true for
+    # scales drawn from U(0.5, 1.5)); weights with larger gains select the online form (running max, lazy
+    # rescale).  A second handle with the bound switched off times that form on the same inputs.
+    bound_log2 = float(128.0 * np.abs(wq).max() * np.abs(wk).max() / np.sqrt(128.0) * 1.4426950408889634)
+    softmax = {"form": "bounded" if bound_log2 <= 40.0 and os.environ.get("KREA_CUDA_STATIC_BOUND", "1") != "0" else "online",
+               "logit_bound_log2": bound_log2, "bound_limit_log2": 40.0}
+    if softmax["form"] == "bounded":
+        os.environ["KREA_CUDA_STATIC_BOUND"] = "0"
+        try:
+            kc2 = ops.KreaCuda(local_rank)
+        finally:
+            del os.environ["KREA_CUDA_STATIC_BOUND"]
+        kc2.set_stream(stream)
+        step2 = make_step(kc2)
+        for i in range(3):
+            step2(i)
+        ms_online = timed_batches(step2, args.steps, 3, stream, ranks)
+        kc2.wait()
+        kc2.close()
+        softmax["online_form_ms_per_step"] = float(np.median(ms_online))
+        softmax["online_form_tflops"] = (flops if by_heads else world * flops) / (softmax["online_form_ms_per_step"] * 1e-3) / 1e12
+
     # ---- end to end through the host-pointer entry point ----
     q_h = qkv_h.view(-1)
     e2e_args = (q_h[h0 * 128:], q_h[(H + h0) * 128:], q_h[(2 * H + h0) * 128:], out_h.view(-1)[h0 * 128:], S, S, Hl, ld, ld, ld, H * 128,
@@ -549,15 +727,34 @@ def run_ours(args, rank, world, local_rank):
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
         kc.joint_attention_host(*e2e_args, **e2e_kw)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        kc.joint_attention_host(*e2e_args, **e2e_kw)
-    torch.cuda.synchronize()
-    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    e2e_batches = []
+    for _ in range(5):
+        ranks.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            kc.joint_attention_host(*e2e_args, **e2e_kw)
+        torch.cuda.synchronize()
+        e2e_batches.append((time.perf_counter() - t0) * 1e3 / e2e_steps)
+    e2e_own_ms = float(np.median(e2e_batches))
+    e2e_batches = ranks.reduce(e2e_batches, "max")
+    e2e_ms = float(np.median(e2e_batches))
     checksum = int(out_h.view(-1)[:: max(1, out_h.numel() // 4096)].to(torch.int64).sum().item())
     h2d = in_bytes * Hl // H + 2 * cos.nbytes + 1024 + (tl.nbytes if tl is not None else 0)
     d2h = out_bytes * Hl // H
+    # achieved host->device rate of the slowest and the fastest rank (the copies overlap the compute, so this
+    # is bytes over the whole call: a lower bound on the link rate)
+    h2d_rate = h2d / (e2e_own_ms * 1e-3) / 1e9
+    h2d_rate_min, = ranks.reduce([h2d_rate], "min")
+    h2d_rate_max, = ranks.reduce([h2d_rate], "max")
+
+    # ---- the two multi-GPU forms of the path, in the same process at every N ----
+    multi = None
+    if cfg.cid == 1 and not by_heads and not args.no_multi:
+        del xs, os_
+        torch.cuda.empty_cache()
+        multi = {"head_split_c3": measure_head_split(kc, 3, max(3, min(args.steps, 10)), 3, 3, ranks, stream),
+                 "seqpar_c4": measure_seq_parallel(kc, max(2, min(args.steps, 5)), 2, 3, ranks, stream, args.a2a),
+                 "note": "strong scaling: one problem over all GPUs; efficiency = ms_per_step(1 GPU) / (N * ms_per_step(N GPUs))"}
 
     if rank == 0:
         peak, peak_sustained, peak_kind = measured_peaks()
@@ -565,23 +762,28 @@ def run_ours(args, rank, world, local_rank):
         value = job_flops / (ms_step * 1e-3) / 1e12
         attn_tflops = job_flops / world / (attn_ms_avg * 1e-3) / 1e12
         line = {
-            "metric": METRIC if cfg.cid == 1 else f"joint-attn TFLOP/s at S={S}, B={B}, 24 heads, head_dim 128", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": "bf16",
+            "metric": METRIC if cfg.cid == 1 else f"joint-attn TFLOP/s at S={S}, B={B}, 24 heads, head_dim 128", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_step, "ms_min": float(min(ms_batches)), "ms_max": float(max(ms_batches)), "timed_batches": REPEATS,
+            "higher_is_better": True, "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": cfg.name, "batch": cfg.batch, "heads": H, "seq": S, "head_dim": 128, "per_gpu": f"heads [{h0}, {h0 + Hl}) of rank 0; {Hl} heads per GPU, no collective" if by_heads else "one full problem (all heads)",
-                       "l2": f"rotating {nsets} input/output sets ({nsets * (in_bytes + out_bytes) / 1e6:.0f} MB > 126 MB L2)",
-                       "flops_per_step_per_gpu": job_flops / world},
+            "config": attention_config(cfg, world, by_heads),
             "pct_of_measured_bf16_peak": 100.0 * value / world / peak,
             "pct_of_nominal_bf16_peak": 100.0 * value / world / 2250.0,
             "gpu_launches": int(launches),
             "clocks": clocks,
             "e2e": {"value": job_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "steps": e2e_steps, "checksum": checksum},
+                    "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_ms, "ms_min": float(min(e2e_batches)), "ms_max": float(max(e2e_batches)),
+                    "steps": e2e_steps, "timed_batches": len(e2e_batches), "checksum": checksum,
+                    "h2d_gbs_per_rank": {"min": h2d_rate_min, "max": h2d_rate_max}},
             "roofline": {"bound": "tensor", "achieved": attn_tflops, "peak": peak, "unit": "TFLOP/s", "frac": attn_tflops / peak,
                          "traffic": ATTN_DRAM_TRAFFIC_BYTES.get(cfg.cid), "peak_kind": f"{peak_kind} burst bf16 GEMM",
                          "frac_of_sustained": attn_tflops / peak_sustained, "kernel": "attn_fwd_sm100", "kernel_ms": attn_ms_avg,
-                         "launches_timed": attn_n, "prologue_kernel_ms": norm_ms / max(norm_n, 1)},
+                         "launches_timed": attn_n, "prologue_kernel_ms": norm_ms / max(norm_n, 1),
+                         "step_minus_kernel_ms": ms_step - attn_ms_avg},
+            "softmax": softmax,
         }
+        if multi is not None:
+            line["multi"] = multi
         if world == 1 and not args.no_cpu:
             heads_sel = list(range(cfg.heads)) if cfg.cid <= 1 else list(range(0, cfg.heads, 6))
             v, secs, threads = cpu_oracle_sample(cfg, heads_sel, repeats=4)
@@ -599,6 +801,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1", choices=sorted(WORKLOADS) + ["block", "gemm", "layerwise"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-multi", action="store_true", help="skip the head-split and sequence-parallel measurements of the default workload")
     ap.add_argument("--shard", default="samples", choices=["samples", "heads"],
                     help="several GPUs, workloads c0-c3: every GPU runs a whole problem (weak scaling), or its share of the heads of one problem (strong)")
     ap.add_argument("--a2a", default="native", choices=["native", "torch"],

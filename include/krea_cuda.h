@@ -58,13 +58,23 @@ KREA_CUDA_API void krea_cuda_destroy(krea_cuda* h);
 /* Message of the last failing call on this handle ("" if none). */
 KREA_CUDA_API const char* krea_cuda_last_error(krea_cuda* h);
 /* Enqueue on the caller's cudaStream_t from now on (NULL = the CUDA default stream).  A new handle
- * starts on a private non-blocking stream of its own. */
+ * starts on a private non-blocking stream of its own.  Changing the stream first waits for the work the
+ * handle queued on the previous one (its workspaces belong to one stream at a time). */
 KREA_CUDA_API int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream);
 /* Wait for the stream (the counterpart of Metal::wait, engine/src/metal.h:57-58) and return
  * KREA_CUDA_E_DEVICE if any kernel since the last sync reported a timed-out wait. */
 KREA_CUDA_API int krea_cuda_sync(krea_cuda* h);
 /* Number of kernels this handle has launched so far. */
 KREA_CUDA_API uint64_t krea_cuda_launch_count(krea_cuda* h);
+/* Every wait inside the attention kernel (on a TMA load, a tensor-core product, another warp) gives up after
+ * this much device time, records where in a status word and lets the CTA run to its normal exit; krea_cuda_sync
+ * then returns KREA_CUDA_E_DEVICE.  Default 2 s; accepted range 1 ms .. 60 s.  No counterpart in the reference
+ * (Metal command buffers are bounded by the system's GPU watchdog instead). */
+KREA_CUDA_API int krea_cuda_set_wait_limit(krea_cuda* h, uint64_t nanoseconds);
+/* Test hook for that path: while on, the attention kernel's producer never requests the last K tile of a CTA,
+ * so the wait for it runs out after the limit above.  Nothing faults and nothing waits longer than the limit;
+ * the output of such a launch is meaningless.  Use with a limit of a few milliseconds. */
+KREA_CUDA_API int krea_cuda_test_drop_one_load(krea_cuda* h, int on);
 /* Per-operator GPU timing, the counterpart of the reference's KREA_PROFILE marks (Metal::mark,
  * engine/src/metal.h:126-145): while enabled, every kernel launch is bracketed by CUDA events on the
  * stream.  krea_cuda_profile_read synchronises the stream and returns the accumulated device time and
@@ -179,9 +189,12 @@ KREA_CUDA_API int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_
  * image: every GPU on which the library is used keeps those 32 MiB reserved until the process exits.
  *  - Limit: batch * Lk * (heads/group) * 256 bytes must fit in the array (e.g. one sample of 24 heads x
  *    5461 keys); larger problems return KREA_CUDA_E_NOMEM with a message and launch nothing.
- *  - The call itself performs no cudaMalloc / cudaFree and calls no allocating library routine.  The first
- *    call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
- *    before any stream capture begins.
+ *  - The call performs no cudaMalloc / cudaFree and calls no allocating library routine, and it does no
+ *    per-device set-up either: krea_cuda_create looks up the array's device address (cudaGetSymbolAddress,
+ *    with the handle's device current - this is the moment the CUDA runtime loads the library's device image
+ *    and the driver sets the 32 MiB aside), loads the two kernels' code and opts the attention kernel in to
+ *    its shared memory (cudaFuncSetAttribute).  So create the handle at start-up, while device memory is
+ *    still to be had and before any stream capture begins; krea_cuda_create fails if that set-up fails.
  *  - All calls, from every handle on the same device, share the one array: it keeps the previous call's
  *    contents (nothing needs clearing - each call overwrites what it reads), and two calls whose kernels
  *    can overlap on the GPU (different streams without ordering) race on it.  Serialise them. */

@@ -107,6 +107,8 @@ SYMBOLS = {
     "krea_cuda_set_stream": (_int, [_vp, _vp]),
     "krea_cuda_sync": (_int, [_vp]),
     "krea_cuda_launch_count": (ctypes.c_uint64, [_vp]),
+    "krea_cuda_set_wait_limit": (_int, [_vp, ctypes.c_uint64]),
+    "krea_cuda_test_drop_one_load": (_int, [_vp, _int]),
     "krea_cuda_profile_enable": (_int, [_vp, _int]),
     "krea_cuda_profile_read": (_int, [_vp, _int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(_int)]),
     "krea_cuda_profile_trace": (_int, [_vp, ctypes.c_char_p]),

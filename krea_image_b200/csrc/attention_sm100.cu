@@ -26,6 +26,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "attention_sm100.h"
@@ -351,7 +352,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           const int kt = tile_of(j);
           const int key0 = kt * BN + part * C::COLS;       // first key of this thread's columns
           KTRACE(trace_me, g * 8 + 0, j);
-          mbar_wait(&s_full[g], j & 1, abort_word, SITE_S);
+          mbar_wait(&s_full[g], j & 1, abort_word, SITE_S, p.wait_limit_ns);
           tc_fence_after();
           KTRACE(trace_me, g * 8 + 1, j);
           uint32_t sv[C::COLS];
@@ -418,7 +419,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           KTRACE(trace_me, g * 8 + 3, j);
           if (j > 0) {
             // P V of the previous key tile still reads P_g (and, for a rescale, writes O_g) until this completes
-            mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV);
+            mbar_wait(&pv_done[g], (j - 1) & 1, abort_word, SITE_PV, p.wait_limit_ns);
             tc_fence_after();
           }
           // p = exp2(s * scale_log2 - m) in packed fp32x2 arithmetic, 32 keys at a time: all the scaling
@@ -495,7 +496,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         named_barrier(bar_id, C::SM_THREADS);
         l_i += slot[part ^ 1];
       }
-      mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV);
+      mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV, p.wait_limit_ns);
       tc_fence_after();
       KTRACE(trace_me, 30 + g, 4);
       const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
@@ -600,7 +601,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const int key0 = tile_of(j) * BN;
         for (int kv = 0; kv < 2; kv++) {
           const int n = 2 * j + kv, stage = n % NSTAGE;
-          const bool ok = mbar_wait(&kv_empty[stage], ((n / NSTAGE) & 1) ^ 1, abort_word, SITE_KV_EMPTY);
+          // test hook: the last K tile is never requested, so the wait for it runs out (its barrier never completes)
+          if (p.test_drop_last_k && kv == 0 && j == n_tiles - 1) continue;
+          const bool ok = mbar_wait(&kv_empty[stage], ((n / NSTAGE) & 1) ^ 1, abort_word, SITE_KV_EMPTY, p.wait_limit_ns);
           if (!ok) break;
           uint8_t* dst = kv_smem + stage * TILE_BYTES;
           mbar_arrive_expect_tx(&kv_full[stage], TILE_BYTES);
@@ -614,10 +617,10 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       if (*abort_word != 0u) {
         // make sure no copy is still in flight into this CTA's shared memory when it exits
         for (int n = max(issued - NSTAGE, 0); n < issued; n++)
-          mbar_wait_slow(&kv_full[n % NSTAGE], (n / NSTAGE) & 1, abort_word + 1, SITE_DRAIN);
+          mbar_wait_slow(&kv_full[n % NSTAGE], (n / NSTAGE) & 1, abort_word + 1, SITE_DRAIN, p.wait_limit_ns);
         if (p.q_tma)
           for (int g = 0; g < NQ; g++)
-            if (q0 + g * BM < p.Lq) mbar_wait_slow(&q_ready[g], 0, abort_word + 1, SITE_DRAIN);
+            if (q0 + g * BM < p.Lq) mbar_wait_slow(&q_ready[g], 0, abort_word + 1, SITE_DRAIN, p.wait_limit_ns);
       }
     }
     } else if (warp == WARP_MMA) {
@@ -679,14 +682,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       uint32_t nqk = 0;        // Q K^T products issued so far == S-tile hand-overs requested
       auto wait_s_free = [&]() {
         if (nqk > 0) {
-          mbar_wait(s_free, (nqk - 1) & 1, abort_word, SITE_S);
+          mbar_wait(s_free, (nqk - 1) & 1, abort_word, SITE_S, p.wait_limit_ns);
           tc_fence_after();
         }
         nqk++;
       };
       for (int g = 0; g < NQ; g++)
-        if (active[g]) mbar_wait(&q_ready[g], 0, abort_word, SITE_Q);
-      mbar_wait(&kv_full[0], 0, abort_word, SITE_KV_FULL);   // K_0
+        if (active[g]) mbar_wait(&q_ready[g], 0, abort_word, SITE_Q, p.wait_limit_ns);
+      mbar_wait(&kv_full[0], 0, abort_word, SITE_KV_FULL, p.wait_limit_ns);   // K_0
       tc_fence_after();
       for (int g = 0; g < NQ; g++)
         if (active[g]) {
@@ -699,8 +702,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const int nv = 2 * j + 1, nk = 2 * j + 2;
         const bool has_next = j + 1 < n_tiles;
         KTRACE(lane == 0, 24, j);
-        if (has_next) mbar_wait(&kv_full[nk % NSTAGE], (nk / NSTAGE) & 1, abort_word, SITE_KV_FULL);
-        mbar_wait(&kv_full[nv % NSTAGE], (nv / NSTAGE) & 1, abort_word, SITE_KV_FULL);
+        if (has_next) mbar_wait(&kv_full[nk % NSTAGE], (nk / NSTAGE) & 1, abort_word, SITE_KV_FULL, p.wait_limit_ns);
+        mbar_wait(&kv_full[nv % NSTAGE], (nv / NSTAGE) & 1, abort_word, SITE_KV_FULL, p.wait_limit_ns);
         KTRACE(lane == 0, 25, j);
         for (int g = 0; g < NQ; g++) {
           if (!active[g]) continue;
@@ -710,7 +713,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             issue_qk(g, nk % NSTAGE);
           }
           KTRACE(lane == 0, 16 + g * 4 + 1, j);
-          mbar_wait(&p_full[g], j & 1, abort_word, SITE_P);
+          mbar_wait(&p_full[g], j & 1, abort_word, SITE_P, p.wait_limit_ns);
           tc_fence_after();
           KTRACE(lane == 0, 16 + g * 4 + 2, j);
           issue_pv(g, nv % NSTAGE, j == 0);
@@ -739,18 +742,30 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   }
 }
 
+// Per-device set-up of one kernel variant (the opt-in to more than 48 KB of dynamic shared memory; under lazy
+// module loading this is also where the device code is loaded).  Done once per device, under a lock: handles
+// on several threads may launch at the same time.
+static std::mutex g_configure_mutex;
+template <int SPLIT, int EMU>
+static cudaError_t configure_impl() {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(g_configure_mutex);
+  if (dev >= 0 && dev < 64 && configured[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(attn_fwd_sm100<SPLIT, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::total + 1024);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64) configured[dev] = true;
+  return cudaSuccess;
+}
+
 template <int SPLIT, int EMU>
 static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const CUtensorMap& tmQ, const AttnParams& p,
                                cudaStream_t stream) {
   const int smem = SmemLayout::total + 1024;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_sm100<SPLIT, EMU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
-  }
+  cudaError_t e = configure_impl<SPLIT, EMU>();
+  if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.Lq + NQ * BM - 1) / (NQ * BM), p.heads, p.batch);
   cfg.blockDim = dim3(Cfg<SPLIT>::THREADS);
@@ -762,6 +777,11 @@ static cudaError_t launch_impl(const CUtensorMap& tmK, const CUtensorMap& tmV, c
   cfg.attrs = attr;
   cfg.numAttrs = p.pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, attn_fwd_sm100<SPLIT, EMU>, tmK, tmV, tmO, tmQ, p);
+}
+
+cudaError_t prepare_attention_sm100(int split, int emu) {
+  if (split == 1) return emu == 1 ? configure_impl<1, 1>() : configure_impl<1, 0>();
+  return emu == 1 ? configure_impl<2, 1>() : configure_impl<2, 0>();
 }
 
 cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const CUtensorMap& tmQ, const AttnParams& p,

@@ -47,6 +47,8 @@ struct AttnParams {
   // griddepcontrol.wait, everything else before it.
   int pdl;
   uint32_t* status;            // device word: 0 = ok, else (site | qblk << 8 | head << 20) of a timed-out wait
+  uint64_t wait_limit_ns;      // bound on every wait inside the kernel (device wall time); 2 s unless a test shortens it
+  int test_drop_last_k;        // test hook: the producer never requests the last K tile, so that a bounded wait runs out
   long long* trace;            // tuning builds only (KREA_ATTN_TRACE): clock64 samples of CTA 0, else nullptr
 };
 
@@ -57,6 +59,10 @@ struct AttnParams {
 // ... and Q when p.q_tma is set.
 cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const CUtensorMap& tmQ, const AttnParams& p,
                                    int split, int emu, cudaStream_t stream);
+
+// The per-device set-up the first launch of that variant would otherwise do (shared-memory opt-in, loading of
+// the device code), for the current device: lets a handle pay for it when it is created.
+cudaError_t prepare_attention_sm100(int split, int emu);
 
 // Out-of-place / in-place per-head RMSNorm + RoPE (qk_norm_rope.cu).
 struct NormRopeParams {
@@ -83,6 +89,8 @@ struct NormRopeParams {
   float bound_scale_log2;      // softmax scale * log2(e)
 };
 cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream);
+// Loads the norm kernels' device code on the current device (what their first launch would otherwise do).
+cudaError_t prepare_qk_norm_rope();
 
 struct ReshardParams {
   const __nv_bfloat16* src;

@@ -15,6 +15,7 @@
 //   * a thread of the epilogue owns one output row (= one TMEM lane), so a head's 128 columns - its sum of
 //     squares, its rotation pairs - are all in that thread's registers: the fused norm needs no exchange;
 //   * every wait is bounded (status word, normal exit) as in the attention kernel.
+#include <mutex>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -391,12 +392,16 @@ static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap
                                        int sms, cudaStream_t stream) {
   using namespace gemm;
   static bool configured[64] = {};
+  static std::mutex configure_mutex;       // handles on several threads may launch at the same time
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(configure_mutex);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;

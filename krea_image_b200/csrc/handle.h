@@ -51,6 +51,8 @@ struct krea_cuda {
   void* block_ws = nullptr;         // intermediates of krea_cuda_dit_block when the caller passes no workspace
   size_t block_ws_bytes = 0;
   void* qw_stage = nullptr;         // pinned staging of krea_cuda_qw_upload (two 8 MiB halves)
+  uint64_t wait_limit_ns = 2000000000ull;   // bound on every wait inside the attention kernel (krea_cuda_set_wait_limit)
+  int test_drop_last_k = 0;         // krea_cuda_test_drop_one_load: the next attention launches never request their last K tile
 };
 
 static inline int fail(krea_cuda* h, int code, const char* fmt, ...) {

@@ -21,6 +21,37 @@
 
 using namespace krea;
 
+// Scratch of krea_cuda_joint_attention_static (the normalised and rotated K that the pre-pass hands to the
+// attention kernel): a fixed array in the library's device image instead of memory obtained at run time.
+// In host code the array's name is only a stand-in for the device symbol - it is not a device address - so
+// the address is looked up per device with cudaGetSymbolAddress (with that device current) and that pointer
+// is what the kernels get.  The lookup is where the CUDA runtime loads this file's device image, i.e. where
+// the driver sets the array's 32 MiB aside on that GPU, so it happens in krea_cuda_create - at start-up, when
+// memory is still there to be had - and never inside a call of the entry point itself.
+static __device__ __align__(256) unsigned char g_static_k_scratch[KREA_CUDA_STATIC_SCRATCH_BYTES];
+static void* g_static_k_scratch_ptr[64] = {};
+static std::mutex g_static_k_scratch_mutex;
+
+// Device address of the array on `device`, which must be the current device.  nullptr + *e on failure.
+static void* static_scratch_on(int device, cudaError_t* e) {
+  *e = cudaSuccess;
+  if (device < 0 || device >= 64) {
+    *e = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_static_k_scratch_mutex);
+  if (g_static_k_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    *e = cudaGetSymbolAddress(&ptr, g_static_k_scratch);
+    if (*e != cudaSuccess || ptr == nullptr) {
+      if (*e == cudaSuccess) *e = cudaErrorInvalidSymbol;
+      return nullptr;
+    }
+    g_static_k_scratch_ptr[device] = ptr;
+  }
+  return g_static_k_scratch_ptr[device];
+}
+
 extern "C" {
 
 krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
@@ -59,6 +90,11 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     ok = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess && fn != nullptr;
     h->encode = (PFN_encodeTiled)fn;
   }
+  if (ok && device < 64) {
+    // resolve the built-in scratch of krea_cuda_joint_attention_static now (see g_static_k_scratch)
+    cudaError_t se;
+    ok = static_scratch_on(device, &se) != nullptr;
+  }
   if (!ok) {
     say("krea_cuda_create: CUDA initialisation failed: ", cudaGetErrorString(cudaGetLastError()));
     krea_cuda_destroy(h);
@@ -80,6 +116,14 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);
     if (v >= 0 && v <= 1) h->emu = v;
+  }
+  // Load the device code of the fused call's two kernels and opt the attention kernel in to its shared memory
+  // now, so that the first call on this device does no set-up of its own (krea_cuda_joint_attention_static
+  // relies on this: nothing may be reserved on the device once its callers have given all memory away).
+  if (prepare_attention_sm100(h->split, h->emu) != cudaSuccess || prepare_qk_norm_rope() != cudaSuccess) {
+    say("krea_cuda_create: kernel set-up failed: ", cudaGetErrorString(cudaGetLastError()));
+    krea_cuda_destroy(h);
+    return nullptr;
   }
   return h;
 }
@@ -116,11 +160,31 @@ const char* krea_cuda_last_error(krea_cuda* h) { return h ? h->err.c_str() : "nu
 
 int krea_cuda_set_stream(krea_cuda* h, void* cuda_stream) {
   if (!h) return KREA_CUDA_E_ARG;
-  h->stream = (cudaStream_t)cuda_stream;
+  cudaStream_t next = (cudaStream_t)cuda_stream;
+  if (next != h->stream) {
+    // Kernels queued on the old stream may still use the handle's workspaces, which later calls on the new
+    // stream may free and re-allocate: let them finish first (the handle's buffers know one stream at a time).
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    CUDA_TRY(h, cudaStreamSynchronize(h->stream));
+  }
+  h->stream = next;
   return KREA_CUDA_OK;
 }
 
 uint64_t krea_cuda_launch_count(krea_cuda* h) { return h ? h->launches : 0; }
+
+int krea_cuda_set_wait_limit(krea_cuda* h, uint64_t ns) {
+  if (!h) return KREA_CUDA_E_ARG;
+  if (ns < 1000000ull || ns > 60000000000ull) return fail(h, KREA_CUDA_E_ARG, "set_wait_limit: the limit must lie between 1 ms and 60 s");
+  h->wait_limit_ns = ns;
+  return KREA_CUDA_OK;
+}
+
+int krea_cuda_test_drop_one_load(krea_cuda* h, int on) {
+  if (!h) return KREA_CUDA_E_ARG;
+  h->test_drop_last_k = on ? 1 : 0;
+  return KREA_CUDA_OK;
+}
 
 int krea_cuda_profile_enable(krea_cuda* h, int on) {
   if (!h) return KREA_CUDA_E_ARG;
@@ -316,6 +380,8 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
   p.logit_bound = (h->static_bound && (c.wq || c.bound_given)) ? c.logit_bound : nullptr;
   p.status = h->status_dev;
+  p.wait_limit_ns = h->wait_limit_ns;
+  p.test_drop_last_k = h->test_drop_last_k;
   p.pdl = c.pdl ? 1 : 0;
   if (c.o_blk != nullptr) {
     if (c.batch != 1 || c.o_blk_rows <= 0 || c.o_blk_n < 1 || c.o_blk_n > 8 || (int64_t)c.o_blk_n * c.o_blk_rows < c.Lq)
@@ -498,15 +564,8 @@ int krea_cuda_joint_attention(krea_cuda* h, const krea_cuda_joint_args* a) {
 }
 
 // ---------------------------------------------------------------------------------------------------
-// The fused call for callers that must not allocate device memory.  Its scratch (the normalised and
-// rotated K that the pre-pass hands to the attention kernel) lives in a fixed array in the library's
-// device image instead of memory obtained at run time.  In host code the array's name is only a
-// stand-in for the device symbol - it is not a device address - so the address is looked up once per
-// device with cudaGetSymbolAddress (with that device current) and that pointer is what the kernels get.
-static __device__ __align__(256) unsigned char g_static_k_scratch[KREA_CUDA_STATIC_SCRATCH_BYTES];
-static void* g_static_k_scratch_ptr[64] = {};
-static std::mutex g_static_k_scratch_mutex;
-
+// The fused call for callers that must not allocate device memory: its scratch is g_static_k_scratch (top of
+// this file), whose device address krea_cuda_create has already resolved for the handle's device.
 int krea_cuda_joint_attention_static(krea_cuda* h, const krea_cuda_joint_args* a) {
   int rc = validate_joint(h, a);
   if (rc) return rc;
@@ -519,19 +578,10 @@ int krea_cuda_joint_attention_static(krea_cuda* h, const krea_cuda_joint_args* a
                 need, (size_t)KREA_CUDA_STATIC_SCRATCH_BYTES);
   if (h->device < 0 || h->device >= 64) return fail(h, KREA_CUDA_E_ARG, "joint_attention_static: device index above 63");
   CUDA_TRY(h, cudaSetDevice(h->device));
-  void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_static_k_scratch_mutex);
-    if (g_static_k_scratch_ptr[h->device] == nullptr) {
-      // first call on this device: resolve the device address of the array (no allocation happens here)
-      void* ptr = nullptr;
-      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_k_scratch);
-      if (e != cudaSuccess || ptr == nullptr)
-        return fail(h, KREA_CUDA_E_CUDA, "joint_attention_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-      g_static_k_scratch_ptr[h->device] = ptr;
-    }
-    scratch = g_static_k_scratch_ptr[h->device];
-  }
+  // already resolved by krea_cuda_create for this device: a table look-up, no CUDA call
+  cudaError_t se;
+  void* scratch = static_scratch_on(h->device, &se);
+  if (scratch == nullptr) return fail(h, KREA_CUDA_E_CUDA, "joint_attention_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(se));
   if (a->Lk == 0) {
     AttnCall c{};
     c.Q = a->Q; c.O = a->O; c.batch = a->batch <= 0 ? 1 : a->batch; c.Lq = a->Lq; c.Lk = 0; c.heads = a->heads; c.group = a->group;
@@ -604,6 +654,8 @@ static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
     for (int cand : {6, 4, 3, 2})   // narrower column blocks than about 1 KB per row slow the DMA down
       if (kvheads % cand == 0) { ngroups = cand; break; }
   }
+  // kv heads per group and the first kv head of every group (uniform unless the list knob below says otherwise)
+  int gheads[8], gfirst[9];
   if (!h->copy_in) {
     CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_in, cudaStreamNonBlocking));
     CUDA_TRY(h, cudaStreamCreateWithFlags(&h->copy_out, cudaStreamNonBlocking));
@@ -616,8 +668,30 @@ static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
   const bool ttrace = getenv("KREA_CUDA_HOST_TRACE") != nullptr;   // tuning aid: print the pipeline's timeline
   cudaEvent_t tev[32] = {};
   if (ttrace) for (int i = 0; i < 32; i++) cudaEventCreate(&tev[i]);
-  const int kvh_g = kvheads / ngroups, hq_g = a->heads / ngroups;     // kv heads / query heads per group
-  const size_t qcw = (size_t)hq_g * 128 * 2, kcw = (size_t)kvh_g * 128 * 2;   // column-block widths in bytes
+  for (int gi = 0; gi < ngroups; gi++) gheads[gi] = kvheads / ngroups;
+  if (const char* e = getenv("KREA_CUDA_HOST_GROUP_HEADS")) {   // tuning knob: kv heads per group, e.g. "8,8,6,2"
+    int n = 0, sum = 0, list[8];
+    for (const char* c = e; *c && n < 8;) {
+      char* end = nullptr;
+      const long v = strtol(c, &end, 10);
+      if (end == c || v < 1) { n = 0; break; }
+      list[n++] = (int)v;
+      sum += (int)v;
+      c = (*end == ',') ? end + 1 : end;
+      if (*end && *end != ',') { n = 0; break; }
+    }
+    if (n >= 1 && sum == kvheads) {
+      ngroups = n;
+      for (int gi = 0; gi < n; gi++) gheads[gi] = list[gi];
+    }
+  }
+  gfirst[0] = 0;
+  for (int gi = 0; gi < ngroups; gi++) gfirst[gi + 1] = gfirst[gi] + gheads[gi];
+  // byte offset / width of group gi's column block in a row of K or V (kv heads) and of Q or O (group query heads per kv head)
+  auto kc0 = [&](int gi) { return (size_t)gfirst[gi] * 128 * 2; };
+  auto kcwf = [&](int gi) { return (size_t)gheads[gi] * 128 * 2; };
+  auto qc0 = [&](int gi) { return (size_t)gfirst[gi] * a->group * 128 * 2; };
+  auto qcwf = [&](int gi) { return (size_t)gheads[gi] * a->group * 128 * 2; };
   // order the copy streams after whatever the caller enqueued on the compute stream
   CUDA_TRY(h, cudaEventRecord(h->pipe_ev[16], h->stream));
   CUDA_TRY(h, cudaStreamWaitEvent(h->copy_in, h->pipe_ev[16], 0));
@@ -625,14 +699,14 @@ static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
   if (ttrace) cudaEventRecord(tev[0], h->copy_in);
   for (int gi = 0; gi < ngroups; gi++) {
     for (int b = 0; b < batch; b++) {
-      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dQ + (size_t)b * a->Lq * qw * 2 + gi * qcw, qw * 2,
-                                    (const char*)a->Q + (size_t)b * a->bsq * 2 + gi * qcw, (size_t)a->ldq * 2, qcw, a->Lq,
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dQ + (size_t)b * a->Lq * qw * 2 + qc0(gi), qw * 2,
+                                    (const char*)a->Q + (size_t)b * a->bsq * 2 + qc0(gi), (size_t)a->ldq * 2, qcwf(gi), a->Lq,
                                     cudaMemcpyHostToDevice, h->copy_in));
-      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dK + (size_t)b * a->Lk * kw * 2 + gi * kcw, kw * 2,
-                                    (const char*)a->K + (size_t)b * a->bsk * 2 + gi * kcw, (size_t)a->ldk * 2, kcw, a->Lk,
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dK + (size_t)b * a->Lk * kw * 2 + kc0(gi), kw * 2,
+                                    (const char*)a->K + (size_t)b * a->bsk * 2 + kc0(gi), (size_t)a->ldk * 2, kcwf(gi), a->Lk,
                                     cudaMemcpyHostToDevice, h->copy_in));
-      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dV + (size_t)b * a->Lk * kw * 2 + gi * kcw, kw * 2,
-                                    (const char*)a->V + (size_t)b * a->bsv * 2 + gi * kcw, (size_t)a->ldv * 2, kcw, a->Lk,
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)dV + (size_t)b * a->Lk * kw * 2 + kc0(gi), kw * 2,
+                                    (const char*)a->V + (size_t)b * a->bsv * 2 + kc0(gi), (size_t)a->ldv * 2, kcwf(gi), a->Lk,
                                     cudaMemcpyHostToDevice, h->copy_in));
     }
     if (gi == 0) {
@@ -679,9 +753,9 @@ static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
   for (int gi = 0; gi < ngroups; gi++) {
     CUDA_TRY(h, cudaStreamWaitEvent(h->stream, h->pipe_ev[gi], 0));
     krea_cuda_joint_args d = *a;
-    d.Q = (char*)dQ + gi * qcw; d.K = (char*)dK + gi * kcw; d.V = (char*)dV + gi * kcw; d.O = (char*)dO + gi * qcw;
+    d.Q = (char*)dQ + qc0(gi); d.K = (char*)dK + kc0(gi); d.V = (char*)dV + kc0(gi); d.O = (char*)dO + qc0(gi);
     d.batch = batch;
-    d.heads = hq_g;
+    d.heads = gheads[gi] * a->group;
     d.ldq = d.ldo = (int)qw; d.ldk = d.ldv = (int)kw;
     d.bsq = d.bso = (int64_t)a->Lq * qw; d.bsk = d.bsv = (int64_t)a->Lk * kw;
     d.wq = (const float*)dW; d.wk = (const float*)dW + 128;
@@ -694,8 +768,8 @@ static int host_pipeline(krea_cuda* h, const krea_cuda_joint_args* a) {
     if (ttrace) cudaEventRecord(tev[10 + gi], h->stream);
     CUDA_TRY(h, cudaStreamWaitEvent(h->copy_out, h->pipe_ev[8 + gi], 0));
     for (int b = 0; b < batch; b++)
-      CUDA_TRY(h, cudaMemcpy2DAsync((char*)a->O + (size_t)b * a->bso * 2 + gi * qcw, (size_t)a->ldo * 2,
-                                    (const char*)dO + (size_t)b * a->Lq * qw * 2 + gi * qcw, qw * 2, qcw, a->Lq,
+      CUDA_TRY(h, cudaMemcpy2DAsync((char*)a->O + (size_t)b * a->bso * 2 + qc0(gi), (size_t)a->ldo * 2,
+                                    (const char*)dO + (size_t)b * a->Lq * qw * 2 + qc0(gi), qw * 2, qcwf(gi), a->Lq,
                                     cudaMemcpyDeviceToHost, h->copy_out));
     if (ttrace) cudaEventRecord(tev[20 + gi], h->copy_out);
   }

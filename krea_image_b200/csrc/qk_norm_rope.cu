@@ -193,6 +193,15 @@ cudaError_t launch_qk_norm_rope(const NormRopeParams& p, cudaStream_t stream) {
   return launch_norm_variant<2, false>(cfg, p);
 }
 
+cudaError_t prepare_qk_norm_rope() {
+  // the three forms the fused call's K pre-pass can take (one per rope mode)
+  cudaFuncAttributes fa;
+  cudaError_t e = cudaFuncGetAttributes(&fa, qk_norm_rope_kernel<0, true>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, qk_norm_rope_kernel<1, true>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, qk_norm_rope_kernel<2, true>);
+  return e;
+}
+
 // ---- sequence <-> head resharding (pack / unpack around an all-to-all) -------------------------------
 // pack:   dst[peer][row][c] = src[row][src_col0 + peer*cols_per_rank + c]
 // unpack: dst[row][dst_col0 + peer*cols_per_rank + c] = src[peer][row][c]      (the inverse of pack)

@@ -44,6 +44,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // the error is reported through the status word in global memory) instead of hanging the GPU.
 // The bound is wall time on the device (%globaltimer), not a poll count, because one try_wait may
 // itself block for an implementation-defined while.
+// A caller may pass a shorter limit (the attention kernel takes it from its parameters, so that a test can make
+// a wait run out in milliseconds).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait in these kernels
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -52,7 +54,8 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-static __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site) {
+static __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site,
+                                                      uint64_t limit_ns = kWaitLimitNs) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -60,16 +63,17 @@ static __device__ __forceinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t pa
       if (*abort_word != 0u) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) break;
+      else if (now - t0 > limit_ns) break;
     }
   }
   atomicCAS((uint32_t*)abort_word, 0u, site);
   return false;
 }
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word, uint32_t site,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, abort_word, site);
+  return mbar_wait_slow(bar, parity, abort_word, site, limit_ns);
 }
 
 // ---- TMA (tile mode, no multicast) -----------------------------------------------------------------

@@ -69,6 +69,14 @@ class KreaCuda:
         """Block until the stream is idle; raises if a kernel reported a timed-out wait."""
         self._check(self.lib.krea_cuda_sync(self.h))
 
+    def set_wait_limit(self, seconds: float):
+        """Bound on every wait inside the attention kernel (default 2 s); a wait that runs out makes wait() raise E_DEVICE."""
+        self._check(self.lib.krea_cuda_set_wait_limit(self.h, int(seconds * 1e9)))
+
+    def test_drop_one_load(self, on: bool):
+        """Test hook: attention launches never request their last K tile, so that a bounded wait runs out."""
+        self._check(self.lib.krea_cuda_test_drop_one_load(self.h, int(on)))
+
     @property
     def launches(self) -> int:
         return int(self.lib.krea_cuda_launch_count(self.h))

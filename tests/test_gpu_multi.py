@@ -5,6 +5,7 @@
 * sequence parallel (Ulysses): rows start sharded, all-to-all to heads, fused call, all-to-all back; every
   rank's rows match the oracle within the parity tolerance - once with torch.distributed carrying the
   all-to-all and once through the library's own NCCL communicator (one C call per step), bit-identical.
+* the host-side watchdog: krea_cuda_dist_sync with a 1 ms limit while every rank's stream is busy.
 """
 import os
 import socket
@@ -30,7 +31,7 @@ def _worker(rank, world, port, out_dir):
 
     import oracle
     from krea_image_b200 import dist as kd
-    from krea_image_b200 import ops, synth
+    from krea_image_b200 import binding, ops, synth
 
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
@@ -110,6 +111,29 @@ def _worker(rank, world, port, out_dir):
         assert torch.equal(back.view(torch.int16), xl[:, :H * 128].contiguous().view(torch.int16))
         kc.dist_shutdown()
         assert kc.dist_size() == 0
+
+        # ---- the watchdog's timeout branch, on a communicator that every rank has joined: no rank is missing and
+        # no collective is in flight; a few milliseconds of ordinary kernels are queued and dist_sync is given 1 ms.
+        # It must report E_TIMEOUT, give the communicator up, and leave the handle serving single-GPU calls.
+        assert kd.init_native(kc) == (rank, world)
+        Sb, Hb = 8192, 8
+        xb = torch.randn((Sb, 3 * Hb * 128), device="cuda").to(torch.bfloat16).view(-1)
+        ob = torch.empty((Sb, Hb * 128), dtype=torch.bfloat16, device="cuda")
+        cb, sb = (dev(t) for t in synth.rope_tables_axial2d(0, 64, 128))
+        ldb = 3 * Hb * 128
+        torch.cuda.synchronize()
+        for _ in range(40):                      # about 0.2 ms each
+            kc.joint_attention(xb, xb[Hb * 128:], xb[2 * Hb * 128:], ob, Sb, Sb, Hb, ldb, ldb, ldb, Hb * 128, d_wq, d_wk, cb, sb)
+        with pytest.raises(ops.KreaCudaError) as e:
+            kc.dist_sync(1)
+        assert e.value.code == binding.E_TIMEOUT, str(e.value)
+        assert kc.dist_size() == 0 and kc.dist_rank() == -1
+        kc.wait()                                # the queued kernels finish; nothing was left waiting on a peer
+        o_again = torch.zeros((S, H * 128), dtype=torch.bfloat16, device="cuda")
+        kc.joint_attention(xf, xf[H * 128:], xf[2 * H * 128:], o_again, S, S, H, ld, ld, ld, H * 128, d_wq, d_wk, d_cos, d_sin)
+        kc.wait()
+        assert torch.equal(o_again.view(torch.int16), o_all.view(torch.int16))
+        kc.dist_shutdown()
         kc.close()
         open(os.path.join(out_dir, f"ok{rank}"), "w").write("ok")
     finally:

@@ -1,6 +1,7 @@
 """The `.qw` weight-file reader (the format that supplies the attention path's QK-norm weights): CPU tests
-of the parser against files written by tests/qw_writer.py, and a GPU test that takes qn / kn from a file
-all the way into the fused attention call."""
+of the parser on contents no converter writes (tests/qw_writer.py) and on damaged copies of a
+converter-written file, and GPU tests that take qn / kn and whole layers from a file all the way into the
+fused attention call and the DiT block.  tests/test_qw_reference_fixture.py pins the format itself."""
 import json
 import os
 import struct
@@ -53,10 +54,8 @@ def test_reader_matches_writer(tmp_path):
 
 
 def test_reader_rejects_damaged_files(tmp_path):
-    rng = np.random.default_rng(4)
-    good = tmp_path / "good.qw"
-    write_qw(good, _model_like(rng, 1))
-    raw = good.read_bytes()
+    # the intact file is one the reference's converter code wrote (tests/golden/make_qw_fixture.py)
+    raw = open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "qw_dit_bf16.qw"), "rb").read()
 
     def expect(name, data, needle):
         p = tmp_path / name

@@ -5,8 +5,9 @@ normalised K in a fixed array inside the library instead of scratch obtained at 
 
 Checked here, through the C ABI: its output equals the allocating entry point's bit for bit (same
 kernels, same data) on two calls in a row with different inputs - the second call finds the first call's
-contents in the shared array - and a problem larger than the built-in array is refused before anything
-is launched.  This file sorts last on purpose, so a run that stops at the first failure has already
+contents in the shared array -, the device's free memory is the same after the calls as before them (the
+handle's creation did every piece of set-up: nothing is reserved inside the call), and a problem larger
+than the built-in array is refused before anything is launched.  This file sorts last on purpose, so a run that stops at the first failure has already
 run every other test."""
 import numpy as np
 import pytest
@@ -32,6 +33,17 @@ def test_static_scratch_entry_matches_allocating_entry_twice():
     kc = ops.KreaCuda(0)
     kc.set_stream(torch.cuda.current_stream())
     try:
+        # The very first use of the fused path on this handle goes through the no-allocation entry point: from
+        # here on (the handle exists, the operands are on the device) the driver must not reserve anything.
+        x, wq, wk, cos, sin = _case(0, 1, 640, 2, 128, 16, 32)
+        first = torch.empty((1, 640, 256), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        free0, _ = torch.cuda.mem_get_info()
+        kc.joint_attention_static(x, x[256:], x[512:], first, 640, 640, 2, 768, 768, 768, 256, wq, wk, cos, sin)
+        kc.wait()
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0, f"the no-allocation entry point changed the device's free memory by {free0 - free1} bytes"
+        assert torch.isfinite(first.float()).all()
         for seed, (B, S, H, T, gh, gw), tl in ((1, (2, 600, 4, 88, 16, 32), [40, 88]), (2, (1, 1536, 6, 512, 32, 32), None)):
             x, wq, wk, cos, sin = _case(seed, B, S, H, T, gh, gw)
             ld = 3 * H * 128

@@ -141,6 +141,20 @@ typedef struct {
 } krea_cuda_attn_args;
 KREA_CUDA_API int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a);
 
+/* Split-K forms of krea_cuda_attention: the reference's attention_d128_first / _mid / _last
+ * (engine/kernels/attention.metal:14-19, 353-370; state at :164-179 and :288-306).  The same loop over ONE block
+ * of keys (K, V and Lk describe the block), with the loop state carried between calls in fp32:
+ *   So [Lq][heads*128] un-normalised output, Sm [Lq][heads] running max (log2 units),
+ *   Sl [Lq][heads][8] partial row sums (their sum is the row sum; this library keeps it in the first of the eight).
+ * FIRST starts from the empty state and stores it, MID loads and stores, LAST loads and writes the normalised
+ * bf16 output (with the gate, if any) like krea_cuda_attention.  Non-causal, one sample, no padding mask.  When
+ * every block but the last holds a multiple of 128 keys the result is bit-identical to one call over all keys.
+ * Q must be the same rows in every call; O (and G) are only used by LAST. */
+#define KREA_CUDA_PART_FIRST 0
+#define KREA_CUDA_PART_MID 1
+#define KREA_CUDA_PART_LAST 2
+KREA_CUDA_API int krea_cuda_attention_partial(krea_cuda* h, const krea_cuda_attn_args* a, int part, float* So, float* Sm, float* Sl);
+
 /* ---- The whole path in one call: DiT::qk_rope + DiT::attend (engine/src/model.mm:271-288) ----
  * Q, K, V are the raw projections (e.g. column blocks of one fused q|k|v row buffer).  Neither input is
  * modified: Q is normalised and rotated inside the attention kernel as it is staged; K is normalised

@@ -9,6 +9,7 @@ import os
 
 from . import build as _build
 
+PART_FIRST, PART_MID, PART_LAST = 0, 1, 2
 OK, E_ARG, E_UNSUPPORTED, E_CUDA, E_DEVICE, E_NOMEM, E_COMM, E_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 ROPE_PAIRS, ROPE_HALF, ROPE_NONE = 0, 1, 2
 EPI_BF16, EPI_QKNORM_ROPE, EPI_RESID_GATE, EPI_SWIGLU, EPI_F32, EPI_GELU, EPI_BIAS_BF16, EPI_BIAS_F32 = 0, 1, 2, 3, 4, 5, 6, 7
@@ -114,6 +115,7 @@ SYMBOLS = {
     "krea_cuda_profile_trace": (_int, [_vp, ctypes.c_char_p]),
     "krea_cuda_qk_norm_rope": (_int, [_vp, ctypes.POINTER(QKNormArgs)]),
     "krea_cuda_attention": (_int, [_vp, ctypes.POINTER(AttnArgs)]),
+    "krea_cuda_attention_partial": (_int, [_vp, ctypes.POINTER(AttnArgs), _int, _vp, _vp, _vp]),
     "krea_cuda_joint_scratch_bytes": (ctypes.c_size_t, [ctypes.POINTER(JointArgs)]),
     "krea_cuda_joint_attention": (_int, [_vp, ctypes.POINTER(JointArgs)]),
     "krea_cuda_joint_attention_host": (_int, [_vp, ctypes.POINTER(JointArgs)]),
@@ -155,7 +157,8 @@ _lib = None
 
 
 def library_path() -> str:
-    return _build.LIB
+    """The in-tree build, unless KREA_CUDA_LIB names another build of the same library (A/B measurements)."""
+    return os.environ.get("KREA_CUDA_LIB") or _build.LIB
 
 
 def load(build_if_missing: bool = True) -> ctypes.CDLL:

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT_DIR, "libkrea_cuda.so")
-SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "qk_norm_rope.cu", "layerwise_attn.cu", "gemm_sm100.cu", "rms_norm.cu", "dequant_q8.cu", "dist_nccl.cu", "qw_file.cu"]
+SOURCES = ["krea_cuda.cu", "attention_sm100.cu", "attention_persist_sm100.cu", "qk_norm_rope.cu", "layerwise_attn.cu", "gemm_sm100.cu", "rms_norm.cu", "dequant_q8.cu", "dist_nccl.cu", "qw_file.cu"]
 HEADERS = ["attention_sm100.h", "sm100_ptx.cuh", "handle.h", os.path.join("..", "..", "include", "krea_cuda.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
@@ -47,6 +47,10 @@ def _check_register_budget(ptxas_log: str) -> None:
         want = expect.get(m.group(2))
         if want is not None and int(m.group(3)) != want:
             raise RuntimeError(f"{m.group(1)} starts with {m.group(3)} registers per thread; setmaxnreg needs {want}")
+    # the persistent kernel: 512 threads, 128 registers each at launch
+    for m in re.finditer(r"Compiling entry function '(\w*attn_persist_sm100\w*)'.*?Used (\d+) registers", ptxas_log, re.S):
+        if int(m.group(2)) != 128:
+            raise RuntimeError(f"{m.group(1)} starts with {m.group(2)} registers per thread; setmaxnreg needs 128")
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

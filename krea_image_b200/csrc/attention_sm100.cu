@@ -38,8 +38,12 @@
 #ifndef KTRACE_Y
 #define KTRACE_Y 0
 #endif
+__device__ long long g_attn_trace[64 * 64];
+extern "C" __attribute__((visibility("default"))) int krea_debug_trace_old(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(g_attn_trace));
+}
 #define KTRACE(cond, slot, j) \
-  do { if ((cond) && blockIdx.x == 0 && blockIdx.y == KTRACE_Y && blockIdx.z == 0 && p.trace && (j) < 64) p.trace[(slot) * 64 + (j)] = clock64(); } while (0)
+  do { if ((cond) && blockIdx.x == 0 && blockIdx.y == KTRACE_Y && blockIdx.z == 0 && (j) < 64) g_attn_trace[(slot) * 64 + (j)] = clock64(); } while (0)
 #else
 #define KTRACE(cond, slot, j) do { } while (0)
 #endif
@@ -91,8 +95,8 @@ struct Cfg {
   static constexpr int COLS = BN / SPLIT;               // score columns per thread
   static constexpr int REGS_SOFTMAX = SPLIT == 1 ? 216 : 104;   // 384 threads start at 168, 640 threads at 96
   static constexpr int REGS_OTHER = SPLIT == 1 ? 72 : 64;
-  static constexpr int REGS_LAUNCH = (NQ * SM_THREADS * REGS_SOFTMAX + 128 * REGS_OTHER) / THREADS;
-  static_assert(REGS_LAUNCH * THREADS == NQ * SM_THREADS * REGS_SOFTMAX + 128 * REGS_OTHER, "register budget must add up");
+  static constexpr int REGS_LAUNCH = (NQ * SM_THREADS * REGS_SOFTMAX + (THREADS - NQ * SM_THREADS) * REGS_OTHER) / THREADS;
+  static_assert(REGS_LAUNCH * THREADS == NQ * SM_THREADS * REGS_SOFTMAX + (THREADS - NQ * SM_THREADS) * REGS_OTHER, "register budget must add up");
 };
 
 // Start of output row `grow` (column 0 of sample 0): O + grow * ldo, or, with the row-block scatter, the
@@ -326,6 +330,23 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           else if (p.rope_mode == 0) stage_q(std::integral_constant<int, 0>{});
           else if (p.rope_mode == 1) stage_q(std::integral_constant<int, 1>{});
           else stage_q(std::integral_constant<int, 2>{});
+          if (SPLIT == 1 && p.state_load) {
+            // split-K continuation (attention.metal:164-179): this row's un-normalised output goes back into its
+            // accumulator before the tensor cores are told that the tile is ready (the first P V then accumulates)
+            const float* so = p.So + ((size_t)min(row, p.Lq - 1) * p.heads + h) * D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              uint32_t ov[32];
+#pragma unroll
+              for (int c = 0; c < 32; c += 4) {
+                const float4 v = __ldg((const float4*)(so + c0 + c));
+                ov[c] = __float_as_uint(v.x); ov[c + 1] = __float_as_uint(v.y); ov[c + 2] = __float_as_uint(v.z); ov[c + 3] = __float_as_uint(v.w);
+              }
+              tmem_st32(tO + c0, ov);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+          }
           fence_proxy_async_smem();
           mbar_arrive(&q_ready[g]);
         }
@@ -340,6 +361,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // the result is the same, and the row-max pass, the vote and the rescale disappear.
       float m_i = -INFINITY;   // running max, log2 units (scaled scores)
       float l_i = 0.f;         // running row sum of exp2(s - m), fp32
+      if (SPLIT == 1 && p.state_load) {
+        const size_t sidx = (size_t)min(row, p.Lq - 1) * p.heads + h;
+        m_i = __ldg(p.Sm + sidx);
+        const float4 la = __ldg((const float4*)(p.Sl + sidx * 8)), lb = __ldg((const float4*)(p.Sl + sidx * 8) + 1);
+        l_i = ((la.x + la.y) + (la.z + la.w)) + ((lb.x + lb.y) + (lb.z + lb.w));
+      }
       const float sc2 = p.scale_log2;
       griddep_wait();          // the logit bound is written by the kernel before this one
       const float bound = p.logit_bound != nullptr ? *(const volatile float*)p.logit_bound : INFINITY;
@@ -411,7 +438,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
               const float alpha = (m_i == -INFINITY) ? 0.f : ex2_approx(m_i - m_new);
               m_i = m_new;
               l_i *= alpha;
-              rescale = j > 0;
+              rescale = j > 0 || (SPLIT == 1 && p.state_load);   // a carried-in accumulator is rescaled like one of this launch
               o_alpha = alpha;
             }
             m_use = (m_i == -INFINITY) ? 0.f : m_i;   // row with no visible key yet: every p is 0
@@ -499,6 +526,29 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       mbar_wait(&pv_done[g], (n_tiles - 1) & 1, abort_word, SITE_PV, p.wait_limit_ns);
       tc_fence_after();
       KTRACE(trace_me, 30 + g, 4);
+      if (SPLIT == 1 && p.state_store) {
+        // split-K hand-over (attention.metal:288-306): the unreduced state instead of the output.  The tensor-memory
+        // loads are warp-wide, so rows past Lq take part in them and only skip the stores.
+        const bool live = row < p.Lq;
+        const size_t sidx = (size_t)min(row, p.Lq - 1) * p.heads + h;
+        float* so = p.So + sidx * D;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t ov[32];
+          tmem_ld32(tO + c0, ov);
+          tmem_wait_ld();
+          if (live) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+              *(float4*)(so + c0 + c) = make_float4(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]), __uint_as_float(ov[c + 2]), __uint_as_float(ov[c + 3]));
+          }
+        }
+        if (live) {
+          p.Sm[sidx] = m_i;
+          *(float4*)(p.Sl + sidx * 8) = make_float4(l_i, 0.f, 0.f, 0.f);
+          *((float4*)(p.Sl + sidx * 8) + 1) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      } else {
       const float inv = l_i > 0.f ? 1.0f / l_i : 0.f;   // attention.metal:316
       const int pos = p.q_row0 + row;
       const bool padded_row = pos >= pad_lo && pos < pad_hi;
@@ -571,6 +621,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           const uint4 v = *(const uint4*)(ostage + rr * 256 + ((ch ^ (rr & 15)) << 4));
           if (grow < p.Lq) *(uint4*)(out_row(p, grow) + ocol) = v;
         }
+      }
       }
       KTRACE(trace_me, 30 + g, 2);
     } else if (tile_active && row < p.Lq && part == 0) {
@@ -646,6 +697,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // can stay on the warp-uniform datapath; only the asynchronous instruction itself is predicated
       // on the elected lane.
       const uint32_t d_s = tmem_base + COL_S;
+      uint32_t nqk = 0;        // Q K^T products issued so far == S-tile hand-overs requested
       auto issue_qk = [&](int g, int stage) {
         const uint32_t qa = q_lo + g * TILE16, kb = (kv_lo + stage * TILE16) | LBO_K;
 #pragma unroll
@@ -679,7 +731,6 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // Issue order: Q K^T of a tile is issued as soon as the shared S tile is free (the other
       // warpgroup has copied its scores out), ahead of the P V that consumes the same tile's previous
       // probabilities, so the tensor pipe always has the next score tile in flight.
-      uint32_t nqk = 0;        // Q K^T products issued so far == S-tile hand-overs requested
       auto wait_s_free = [&]() {
         if (nqk > 0) {
           mbar_wait(s_free, (nqk - 1) & 1, abort_word, SITE_S, p.wait_limit_ns);
@@ -716,7 +767,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
           mbar_wait(&p_full[g], j & 1, abort_word, SITE_P, p.wait_limit_ns);
           tc_fence_after();
           KTRACE(lane == 0, 16 + g * 4 + 2, j);
-          issue_pv(g, nv % NSTAGE, j == 0);
+          issue_pv(g, nv % NSTAGE, j == 0 && !p.state_load);
           KTRACE(lane == 0, 16 + g * 4 + 3, j);
         }
         if (leader) {

@@ -47,6 +47,13 @@ struct AttnParams {
   // griddepcontrol.wait, everything else before it.
   int pdl;
   uint32_t* status;            // device word: 0 = ok, else (site | qblk << 8 | head << 20) of a timed-out wait
+  // Split-K state (attention.metal:14-19): fp32 So [Lq][heads*128] un-normalised output, Sm [Lq][heads] running max
+  // (log2 units), Sl [Lq][heads][8] partial row sums (their sum is the row sum).  state_load: start from it instead
+  // of the empty state; state_store: leave it instead of the normalised bf16 output.  One-item kernel only.
+  float* So;
+  float* Sm;
+  float* Sl;
+  int state_load, state_store;
   uint64_t wait_limit_ns;      // bound on every wait inside the kernel (device wall time); 2 s unless a test shortens it
   int test_drop_last_k;        // test hook: the producer never requests the last K tile, so that a bounded wait runs out
   long long* trace;            // tuning builds only (KREA_ATTN_TRACE): clock64 samples of CTA 0, else nullptr
@@ -59,6 +66,14 @@ struct AttnParams {
 // ... and Q when p.q_tma is set.
 cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmO, const CUtensorMap& tmQ, const AttnParams& p,
                                    int split, int emu, cudaStream_t stream);
+
+// The persistent form of the same kernel (attention_persist_sm100.cu): one CTA per SM walks over the (query block,
+// head, sample) items, a fourth warpgroup stages the next item's Q and writes the previous item's output while the
+// tensor pipe keeps running.  Same parameters and results; `sms` = SMs of the device (the grid never exceeds it).
+// p.o_tma is ignored (the output rows are stored straight from registers), tmQ is used when p.q_tma is set.
+cudaError_t launch_attention_persist_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmQ, const AttnParams& p, int emu,
+                                           int sms, cudaStream_t stream);
+cudaError_t prepare_attention_persist_sm100(int emu);
 
 // The per-device set-up the first launch of that variant would otherwise do (shared-memory opt-in, loading of
 // the device code), for the current device: lets a handle pay for it when it is created.

@@ -106,6 +106,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     if (v == 1 || v == 2) h->split = v;
   }
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
+  if (const char* s = getenv("KREA_CUDA_PERSIST")) h->persist = atoi(s) != 0;             // tuning knob: persistent attention kernel
   if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_O_TMA")) h->o_tma = atoi(s) != 0;                 // tuning knob
   if (const char* s = getenv("KREA_CUDA_Q_TMA")) h->q_tma = atoi(s) != 0;                 // tuning knob
@@ -120,7 +121,13 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   // Load the device code of the fused call's two kernels and opt the attention kernel in to its shared memory
   // now, so that the first call on this device does no set-up of its own (krea_cuda_joint_attention_static
   // relies on this: nothing may be reserved on the device once its callers have given all memory away).
-  if (prepare_attention_sm100(h->split, h->emu) != cudaSuccess || prepare_qk_norm_rope() != cudaSuccess) {
+  if (h->split != 1) h->persist = false;   // the persistent kernel has one softmax thread per row
+  {
+    cudaDeviceProp prop2;
+    if (cudaGetDeviceProperties(&prop2, device) == cudaSuccess) h->sm_count = prop2.multiProcessorCount;
+  }
+  if ((h->persist ? prepare_attention_persist_sm100(h->emu) : prepare_attention_sm100(h->split, h->emu)) != cudaSuccess ||
+      prepare_qk_norm_rope() != cudaSuccess) {
     say("krea_cuda_create: kernel set-up failed: ", cudaGetErrorString(cudaGetLastError()));
     krea_cuda_destroy(h);
     return nullptr;
@@ -345,6 +352,8 @@ struct AttnCall {
   bool bound_given;     // logit_bound holds for Q and K as they are (normalised by an earlier kernel)
   void* const* o_blk;   // row-block scatter of the output (see AttnParams::O_blk), nullptr = none
   int o_blk_n, o_blk_rows;
+  float *So, *Sm, *Sl;  // split-K state (krea_cuda_attention_partial), nullptr = none
+  bool state_load, state_store;
 };
 
 static int run_attention(krea_cuda* h, const AttnCall& c) {
@@ -379,6 +388,9 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.wq = c.wq; p.cos = c.cos; p.sin = c.sin; p.eps = c.eps; p.rope_mode = c.rope_mode; p.q_row0 = c.q_row0;
   p.text_len = c.text_len; p.text_slots = c.text_len ? c.text_slots : 0;
   p.logit_bound = (h->static_bound && (c.wq || c.bound_given)) ? c.logit_bound : nullptr;
+  p.So = c.So; p.Sm = c.Sm; p.Sl = c.Sl;
+  p.state_load = c.state_load ? 1 : 0; p.state_store = c.state_store ? 1 : 0;
+  const bool partial = c.state_load || c.state_store;     // the split-K forms live in the one-item kernel
   p.status = h->status_dev;
   p.wait_limit_ns = h->wait_limit_ns;
   p.test_drop_last_k = h->test_drop_last_k;
@@ -398,7 +410,7 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   memset(&tmV, 0, sizeof(tmV));
   memset(&tmO, 0, sizeof(tmO));
   memset(&tmQ, 0, sizeof(tmQ));
-  if (h->q_tma && c.wq == nullptr && c.Lk > 0) {
+  if (h->q_tma && c.wq == nullptr && c.Lk > 0 && !partial) {
     // no prologue: Q goes from global to the MMA's shared-memory layout by TMA, no thread touches it
     int rc = make_kv_map(h, &tmQ, c.Q, c.heads * 128, c.Lq, c.batch, c.ldq, c.bsq, "Q");
     if (rc) return rc;
@@ -418,7 +430,8 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   }
   {
     ProfileMark pm(h, 1);
-    CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, tmQ, p, h->split, h->emu, h->stream));
+    if (h->persist && h->sm_count > 0 && !partial) CUDA_TRY(h, launch_attention_persist_sm100(tmK, tmV, tmQ, p, h->emu, h->sm_count, h->stream));
+    else CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, tmQ, p, partial ? 1 : h->split, h->emu, h->stream));
   }
   h->launches++;
   return KREA_CUDA_OK;
@@ -441,6 +454,30 @@ int krea_cuda_attention(krea_cuda* h, const krea_cuda_attn_args* a) {
   c.text_len = a->text_len; c.text_slots = a->text_slots;
   c.causal = a->causal; c.q_pos0 = a->q_pos0;
   c.QB = big ? a->QB : nullptr; c.KB = big ? a->KB : nullptr;
+  return run_attention(h, c);
+}
+
+int krea_cuda_attention_partial(krea_cuda* h, const krea_cuda_attn_args* a, int part, float* So, float* Sm, float* Sl) {
+  if (!h || !a) return fail(h, KREA_CUDA_E_ARG, "attention_partial: null handle or arguments");
+  if (part < KREA_CUDA_PART_FIRST || part > KREA_CUDA_PART_LAST) return fail(h, KREA_CUDA_E_ARG, "attention_partial: part must be FIRST, MID or LAST");
+  if (!So || !Sm || !Sl || !aligned16(So) || !aligned16(Sl) || ((uintptr_t)Sm & 3u)) return fail(h, KREA_CUDA_E_ARG, "attention_partial: null or misaligned state");
+  // the reference's split kernels are non-causal (attention.metal:14) and, like every operator of it, unbatched
+  if (a->causal) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention_partial: the split-K forms are non-causal");
+  if (a->batch > 1 || a->text_len) return fail(h, KREA_CUDA_E_UNSUPPORTED, "attention_partial: no batch and no padding mask");
+  if (a->Lk <= 0) return fail(h, KREA_CUDA_E_ARG, "attention_partial: a key block must hold at least one key");
+  const bool big = a->QB && a->KB;
+  AttnCall c{};
+  c.Q = a->Q; c.K = a->K; c.V = a->V; c.O = a->O;
+  c.G = (part == KREA_CUDA_PART_LAST && a->G && a->ldg > 0) ? a->G : nullptr;   // the gate belongs to the store of the output
+  c.batch = 1;
+  c.Lq = a->Lq; c.Lk = a->Lk; c.heads = a->heads; c.group = a->group;
+  c.ldq = a->ldq; c.ldk = a->ldk; c.ldv = a->ldv; c.ldo = a->ldo; c.ldg = c.G ? a->ldg : 0;
+  c.rope_mode = KREA_CUDA_ROPE_NONE;
+  c.QB = big ? a->QB : nullptr; c.KB = big ? a->KB : nullptr;
+  c.So = So; c.Sm = Sm; c.Sl = Sl;
+  c.state_load = part != KREA_CUDA_PART_FIRST;
+  c.state_store = part != KREA_CUDA_PART_LAST;
+  if (part != KREA_CUDA_PART_LAST && !c.O) c.O = So;   // never written by these parts; run_attention wants a pointer
   return run_attention(h, c);
 }
 

@@ -291,6 +291,15 @@ __device__ __forceinline__ uint64_t exp2_emulated_x2(uint64_t x2) {
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// 32 bytes to global memory in one instruction (the address must be 32-byte aligned).  A thread that writes its own
+// row piece by piece fills whole 32-byte sectors this way: a 16-byte store leaves half a sector for the L2 to fetch
+// from memory first, and a few thousand such fills in flight per SM stall the stores for thousands of clocks.
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]),
+               "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // ---- small math helpers ----------------------------------------------------------------------------
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;

@@ -110,6 +110,13 @@ class KreaCuda:
                        text_slots, q_row0)
         self._check(self.lib.krea_cuda_attention(self.h, ctypes.byref(a)))
 
+    def attention_partial(self, part, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, So, Sm, Sl, group=1, G=None, ldg=0, QB=None, KB=None):
+        """attention_d128_first / _mid / _last (engine/kernels/attention.metal:353-370): part = 0 / 1 / 2; K, V, Lk describe
+        one block of keys; So f32 [Lq, heads*128], Sm f32 [Lq, heads], Sl f32 [Lq, heads, 8] carry the loop state."""
+        a = B.AttnArgs(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), Lq, Lk, heads, ldq, ldk, ldv, ldo, group, 0, 0, _ptr(G), ldg,
+                       _ptr(QB), _ptr(KB), 1, 0, 0, 0, 0, 0, None, 0, 0)
+        self._check(self.lib.krea_cuda_attention_partial(self.h, ctypes.byref(a), int(part), _ptr(So), _ptr(Sm), _ptr(Sl)))
+
     # ---- DiT::qk_rope + DiT::attend in one call (engine/src/model.mm:271-288) -----------------------
     def _joint_args(self, Q, K, V, O, Lq, Lk, heads, ldq, ldk, ldv, ldo, wq, wk, cos, sin, eps, group, rope_mode, q_row0,
                     batch, bsq, bsk, bsv, bso, text_len, text_slots, G, ldg, bsg, k_scratch, k_scratch_bytes):

@@ -264,6 +264,49 @@ def test_attention_gate(kc):
     check(host_f32(o), want, None, "gated attention")
 
 
+@pytest.mark.parametrize("cuts,exact", [((256, 512), True), ((384,), True), ((200, 500), False), ((128, 256, 384, 512, 640), True)])
+def test_split_k_parts_equal_one_pass(kc, cuts, exact):
+    """attention_d128_first / _mid / _last (attention.metal:14-19, 353-370): the loop over key blocks with the state
+    (un-normalised O, running max, row sums) carried between launches in fp32.  Blocks that are multiples of 128
+    keys reproduce the single pass bit for bit; any other split stays within the parity tolerance.  GQA, a ragged
+    query tail and the gate (applied by the last part only) are included."""
+    rng = np.random.default_rng(61 + len(cuts))
+    Lq, Lk, H, group = 300, 700, 4, 2
+    kvh = H // group
+    ldq, ldk, ldg = H * 128, kvh * 128, H * 128
+    Q, G = (synth.f32_to_bf16_bits(rng.standard_normal((Lq, ldq)).astype(np.float32)) for _ in range(2))
+    K, V = (synth.f32_to_bf16_bits((rng.standard_normal((Lk, ldk)) * 1.5).astype(np.float32)) for _ in range(2))
+    want = oracle.attention(Q, K, V, Lq, Lk, H, ldq, ldk, ldk, group=group, G=G, ldg=ldg)
+    dQ, dK, dV, dG = dev_bits(Q), dev_bits(K), dev_bits(V), dev_bits(G)
+    one = torch.zeros((Lq, ldq), dtype=torch.bfloat16, device="cuda")
+    kc.attention(dQ, dK, dV, one, Lq, Lk, H, ldq, ldk, ldk, ldq, group, False, 0, dG, ldg)
+    So = torch.full((Lq, H * 128), float("nan"), dtype=torch.float32, device="cuda")
+    Sm = torch.full((Lq, H), float("nan"), dtype=torch.float32, device="cuda")
+    Sl = torch.full((Lq, H, 8), float("nan"), dtype=torch.float32, device="cuda")
+    out = torch.zeros((Lq, ldq), dtype=torch.bfloat16, device="cuda")
+    edges = [0, *cuts, Lk]
+    n0 = kc.launches
+    for i, (lo, hi) in enumerate(zip(edges[:-1], edges[1:])):
+        part = binding.PART_FIRST if i == 0 else binding.PART_LAST if hi == Lk else binding.PART_MID
+        kc.attention_partial(part, dQ, dK.view(-1)[lo * ldk:], dV.view(-1)[lo * ldk:], out, Lq, hi - lo, H, ldq, ldk, ldk, ldq, So, Sm, Sl,
+                             group=group, G=dG, ldg=ldg)
+        if part != binding.PART_LAST:
+            kc.wait()
+            assert torch.isfinite(So).all() and torch.isfinite(Sl).all() and not torch.isnan(Sm).any()
+            assert torch.equal(out, torch.zeros_like(out))            # only the last part writes the output
+    kc.wait()
+    assert kc.launches - n0 == len(edges) - 1
+    check(host_f32(out), want, None, f"split-K at {cuts}")
+    if exact:
+        assert torch.equal(out.view(torch.int16), one.view(torch.int16))
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.attention_partial(binding.PART_MID, dQ, dK, dV, out, Lq, 0, H, ldq, ldk, ldk, ldq, So, Sm, Sl, group=group)
+    assert e.value.code == binding.E_ARG
+    with pytest.raises(ops.KreaCudaError) as e:
+        kc.attention_partial(3, dQ, dK, dV, out, Lq, Lk, H, ldq, ldk, ldk, ldq, So, Sm, Sl, group=group)
+    assert e.value.code == binding.E_ARG
+
+
 def test_gate_extremes_saturate_cleanly(kc):
     """The sigmoid gate runs on the approximate exp2 and reciprocal of the special-function unit: gates far outside
     the usual range (and +-inf, which bf16 can hold) must give exactly 0 or the ungated value, never NaN."""
@@ -481,11 +524,15 @@ def test_sequence_parallel_entry_points_on_one_rank(kc):
 
 @pytest.mark.parametrize("env", [{"KREA_CUDA_SPLIT": "2"}, {"KREA_CUDA_EMU": "1"}, {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_EMU": "1"},
                                  {"KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PDL": "0"}, {"KREA_CUDA_O_TMA": "0"},
-                                 {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_O_TMA": "0", "KREA_CUDA_PDL": "0"}])
+                                 {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_O_TMA": "0", "KREA_CUDA_PDL": "0"},
+                                 {"KREA_CUDA_PERSIST": "0"}, {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_EMU": "1"},
+                                 {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_O_TMA": "0"},
+                                 {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_PDL": "0"}, {"KREA_CUDA_Q_TMA": "0"}])
 def test_tuning_knob_variants(monkeypatch, env):
-    """The build-time variants a handle can select through its environment (two softmax threads per row,
-    polynomial exp2 for a quarter of the elements, online max instead of the a-priori bound, plain instead
-    of programmatic launch, copy loop instead of TMA output stores) give the same results within tolerance, including a ragged key tail, GQA and the padding mask."""
+    """The build-time variants a handle can select through its environment (the one-item-per-CTA kernel instead
+    of the persistent one, two softmax threads per row, polynomial exp2 for a quarter of the elements, online max
+    instead of the a-priori bound, plain instead of programmatic launch, copy loop instead of TMA output stores)
+    give the same results within tolerance, including a ragged key tail, GQA and the padding mask."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
     k2 = ops.KreaCuda(0)

@@ -33,7 +33,8 @@ struct krea_cuda {
   PFN_encodeTiled encode = nullptr;
   int split = 1;                    // softmax threads per query row
   int emu = 0;                      // 1: one of every 4 element pairs takes the polynomial exp2
-  bool persist = true;              // attention runs as the persistent kernel (one CTA per SM walking over the items)
+  int persist = 1;                  // persistent attention kernel (one CTA per SM walking over the work items):
+                                    // 0 never, 1 when there are more items than SMs, 2 always
   bool pdl = true;                  // fused call: pre-pass and attention use programmatic dependent launch
   bool q_tma = true;                // plain attention operator: Q tiles arrive as TMA loads
   bool o_tma = true;                // attention output tiles leave shared memory as TMA stores

@@ -106,7 +106,10 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     if (v == 1 || v == 2) h->split = v;
   }
   if (const char* s = getenv("KREA_CUDA_STATIC_BOUND")) h->static_bound = atoi(s) != 0;   // tuning knob
-  if (const char* s = getenv("KREA_CUDA_PERSIST")) h->persist = atoi(s) != 0;             // tuning knob: persistent attention kernel
+  if (const char* s = getenv("KREA_CUDA_PERSIST")) {  // tuning knob: persistent attention kernel never / by problem size / always
+    const int v = atoi(s);
+    if (v >= 0 && v <= 2) h->persist = v;
+  }
   if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_O_TMA")) h->o_tma = atoi(s) != 0;                 // tuning knob
   if (const char* s = getenv("KREA_CUDA_Q_TMA")) h->q_tma = atoi(s) != 0;                 // tuning knob
@@ -121,12 +124,12 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   // Load the device code of the fused call's two kernels and opt the attention kernel in to its shared memory
   // now, so that the first call on this device does no set-up of its own (krea_cuda_joint_attention_static
   // relies on this: nothing may be reserved on the device once its callers have given all memory away).
-  if (h->split != 1) h->persist = false;   // the persistent kernel has one softmax thread per row
+  if (h->split != 1) h->persist = 0;       // the persistent kernel has one softmax thread per row
   {
     cudaDeviceProp prop2;
     if (cudaGetDeviceProperties(&prop2, device) == cudaSuccess) h->sm_count = prop2.multiProcessorCount;
   }
-  if ((h->persist ? prepare_attention_persist_sm100(h->emu) : prepare_attention_sm100(h->split, h->emu)) != cudaSuccess ||
+  if ((h->persist ? prepare_attention_persist_sm100(h->emu) : cudaSuccess) != cudaSuccess || prepare_attention_sm100(h->split, h->emu) != cudaSuccess ||
       prepare_qk_norm_rope() != cudaSuccess) {
     say("krea_cuda_create: kernel set-up failed: ", cudaGetErrorString(cudaGetLastError()));
     krea_cuda_destroy(h);
@@ -430,7 +433,11 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   }
   {
     ProfileMark pm(h, 1);
-    if (h->persist && h->sm_count > 0 && !partial) CUDA_TRY(h, launch_attention_persist_sm100(tmK, tmV, tmQ, p, h->emu, h->sm_count, h->stream));
+    // One CTA per SM walking over its work items pays when there is more than one item per CTA; a problem that
+    // fits the SMs in one wave runs the one-item kernel (measured at 120 items: 4 % faster).
+    const long long items = (long long)((c.Lq + 255) / 256) * c.heads * c.batch;
+    const bool persist = h->persist != 0 && h->sm_count > 0 && !partial && (h->persist == 2 || items > h->sm_count);
+    if (persist) CUDA_TRY(h, launch_attention_persist_sm100(tmK, tmV, tmQ, p, h->emu, h->sm_count, h->stream));
     else CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, tmQ, p, partial ? 1 : h->split, h->emu, h->stream));
   }
   h->launches++;

@@ -22,9 +22,17 @@ MAX_ABS_TOL = 2e-2    # vs fp32 oracle
 REL_L2_REF = 4e-3
 
 
-@pytest.fixture(scope="module")
-def kc():
-    k = ops.KreaCuda(0)
+@pytest.fixture(scope="module", params=["by-size", "persistent"])
+def kc(request):
+    """Every test of this module runs twice: with the library choosing between its two attention kernels by
+    problem size (these cases mostly fit the SMs in one wave and take the one-item kernel), and with the
+    persistent kernel forced, so that its item walk sees the same ragged, padded, grouped and batched cases."""
+    if request.param == "persistent":
+        os.environ["KREA_CUDA_PERSIST"] = "2"
+    try:
+        k = ops.KreaCuda(0)
+    finally:
+        os.environ.pop("KREA_CUDA_PERSIST", None)
     k.set_stream(torch.cuda.current_stream())
     yield k
     k.close()
@@ -527,7 +535,10 @@ def test_sequence_parallel_entry_points_on_one_rank(kc):
                                  {"KREA_CUDA_SPLIT": "2", "KREA_CUDA_O_TMA": "0", "KREA_CUDA_PDL": "0"},
                                  {"KREA_CUDA_PERSIST": "0"}, {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_EMU": "1"},
                                  {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_O_TMA": "0"},
-                                 {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_PDL": "0"}, {"KREA_CUDA_Q_TMA": "0"}])
+                                 {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_PDL": "0"}, {"KREA_CUDA_Q_TMA": "0"},
+                                 {"KREA_CUDA_PERSIST": "2"}, {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_EMU": "1"},
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_PDL": "0"},
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_Q_TMA": "0"}])
 def test_tuning_knob_variants(monkeypatch, env):
     """The build-time variants a handle can select through its environment (the one-item-per-CTA kernel instead
     of the persistent one, two softmax threads per row, polynomial exp2 for a quarter of the elements, online max

@@ -12,7 +12,9 @@ from krea_image_b200 import binding, ops, synth
 pytestmark = pytest.mark.gpu
 
 
-def test_a_wait_that_runs_out_is_reported_and_the_handle_recovers():
+@pytest.mark.parametrize("persist", ["0", "2"])     # the one-item kernel and the persistent one (forced on this small case)
+def test_a_wait_that_runs_out_is_reported_and_the_handle_recovers(monkeypatch, persist):
+    monkeypatch.setenv("KREA_CUDA_PERSIST", persist)
     kc = ops.KreaCuda(0)
     kc.set_stream(torch.cuda.current_stream())
     try:

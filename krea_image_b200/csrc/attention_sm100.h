@@ -47,6 +47,21 @@ struct AttnParams {
   // griddepcontrol.wait, everything else before it.
   int pdl;
   uint32_t* status;            // device word: 0 = ok, else (site | qblk << 8 | head << 20) of a timed-out wait
+  // K normalised inside the persistent kernel (an option of the fused call; Kraw == nullptr: K was normalised by an
+  // earlier kernel).  Every work item whose head is the first of its group normalises and rotates one slice of the
+  // key rows of its (sample, kv head) - rows [query block * k_slice_rows, + k_slice_rows) - from Kraw into Kn, the
+  // array the K tensor map describes, and adds 16 to kcount[sample * kv heads + kv head]; a CTA asks for the keys of
+  // a (sample, kv head) once that counter has reached 16 * k_slices.  kcount is zero at launch; the launch also
+  // zeroes kcount_clear (the next launch's counters).
+  const __nv_bfloat16* Kraw;
+  int64_t ldkr, bskr;          // raw K: row stride, sample stride (elements)
+  const float* wk;
+  __nv_bfloat16* Kn;           // [batch][Lk][kv heads * 128]
+  uint32_t* kcount;
+  uint32_t* kcount_clear;
+  int kcount_clear_n;
+  int k_slices, k_slice_rows;
+  int bound_in_kernel;         // the kernel works the logit bound out of wq and wk itself (else: online softmax)
   // Split-K state (attention.metal:14-19): fp32 So [Lq][heads*128] un-normalised output, Sm [Lq][heads] running max
   // (log2 units), Sl [Lq][heads][8] partial row sums (their sum is the row sum).  state_load: start from it instead
   // of the empty state; state_store: leave it instead of the normalised bf16 output.  One-item kernel only.
@@ -73,7 +88,7 @@ cudaError_t launch_attention_sm100(const CUtensorMap& tmK, const CUtensorMap& tm
 // p.o_tma is ignored (the output rows are stored straight from registers), tmQ is used when p.q_tma is set.
 cudaError_t launch_attention_persist_sm100(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmQ, const AttnParams& p, int emu,
                                            int sms, cudaStream_t stream);
-cudaError_t prepare_attention_persist_sm100(int emu);
+cudaError_t prepare_attention_persist_sm100(int emu, bool keys_inside);
 
 // The per-device set-up the first launch of that variant would otherwise do (shared-memory opt-in, loading of
 // the device code), for the current device: lets a handle pay for it when it is created.

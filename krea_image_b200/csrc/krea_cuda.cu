@@ -81,8 +81,9 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   h->device = device;
   bool ok = cudaSetDevice(device) == cudaSuccess;
   ok = ok && cudaStreamCreateWithFlags(&h->own_stream, cudaStreamNonBlocking) == cudaSuccess;
-  ok = ok && cudaMalloc((void**)&h->status_dev, 256) == cudaSuccess;
-  ok = ok && cudaMemset(h->status_dev, 0, 256) == cudaSuccess;
+  const size_t status_bytes = 256 + 2 * (size_t)krea_cuda::kKeyCounters * 4;
+  ok = ok && cudaMalloc((void**)&h->status_dev, status_bytes) == cudaSuccess;
+  ok = ok && cudaMemset(h->status_dev, 0, status_bytes) == cudaSuccess;
   ok = ok && cudaMallocHost((void**)&h->status_host, 256) == cudaSuccess;
   if (ok) {
     void* fn = nullptr;
@@ -110,6 +111,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     const int v = atoi(s);
     if (v >= 0 && v <= 2) h->persist = v;
   }
+  if (const char* s = getenv("KREA_CUDA_KFUSE")) h->kfuse = atoi(s) != 0;                 // option: K normalised inside the attention kernel
   if (const char* s = getenv("KREA_CUDA_PDL")) h->pdl = atoi(s) != 0;                     // tuning knob
   if (const char* s = getenv("KREA_CUDA_O_TMA")) h->o_tma = atoi(s) != 0;                 // tuning knob
   if (const char* s = getenv("KREA_CUDA_Q_TMA")) h->q_tma = atoi(s) != 0;                 // tuning knob
@@ -129,7 +131,8 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
     cudaDeviceProp prop2;
     if (cudaGetDeviceProperties(&prop2, device) == cudaSuccess) h->sm_count = prop2.multiProcessorCount;
   }
-  if ((h->persist ? prepare_attention_persist_sm100(h->emu) : cudaSuccess) != cudaSuccess || prepare_attention_sm100(h->split, h->emu) != cudaSuccess ||
+  if ((h->persist ? prepare_attention_persist_sm100(h->emu, false) : cudaSuccess) != cudaSuccess ||
+      (h->persist && h->kfuse ? prepare_attention_persist_sm100(h->emu, true) : cudaSuccess) != cudaSuccess || prepare_attention_sm100(h->split, h->emu) != cudaSuccess ||
       prepare_qk_norm_rope() != cudaSuccess) {
     say("krea_cuda_create: kernel set-up failed: ", cudaGetErrorString(cudaGetLastError()));
     krea_cuda_destroy(h);
@@ -357,7 +360,43 @@ struct AttnCall {
   int o_blk_n, o_blk_rows;
   float *So, *Sm, *Sl;  // split-K state (krea_cuda_attention_partial), nullptr = none
   bool state_load, state_store;
+  // fused call with K normalised inside the attention kernel: the caller's K (K above is then the scratch that
+  // receives the normalised keys), nullptr = K is final as it is
+  const void* Kraw;
+  int64_t ldkr, bskr;
+  const float* wk;
 };
+
+// Query blocks (work items per head) of the attention kernels, and the key rows each of them normalises when K is
+// normalised inside the persistent kernel.
+static inline int attn_query_blocks(int Lq) { return (Lq + 255) / 256; }
+static inline int key_slice_rows(int Lq, int Lk) { const int n = attn_query_blocks(Lq); return (Lk + n - 1) / n; }
+// whether a problem runs as the persistent kernel: one CTA per SM walking over its work items pays when there is
+// more than one item per CTA; a problem that fits the SMs in one wave runs the one-item kernel (measured at 120
+// items: 4 % faster)
+static inline bool runs_persistent(const krea_cuda* h, int batch, int heads, int Lq) {
+  const long long items = (long long)attn_query_blocks(Lq) * heads * batch;
+  return h->persist != 0 && h->sm_count > 0 && (h->persist == 2 || items > h->sm_count);
+}
+
+// Whether the fused call normalises K inside the persistent kernel (the handle's option, and a shape that allows
+// it).  The keys of a (sample, kv head) are spread over the query blocks of one head; a CTA that waits for them must
+// find every such block among the items that its neighbours have already passed or hold now, which is so when a
+// head has no more blocks than there are CTAs.
+static bool fuse_keys(const krea_cuda* h, const krea_cuda_joint_args* a) {
+  if (!h->kfuse || a->Lk <= 0) return false;
+  const int batch = a->batch <= 0 ? 1 : a->batch;
+  if (!runs_persistent(h, batch, a->heads, a->Lq)) return false;
+  const int nqb = attn_query_blocks(a->Lq);
+  if (nqb > h->sm_count) return false;
+  // a CTA with three or more items leaves the later key slices to two of its warps, which keep up with the
+  // attention only when a head has enough query blocks to share its keys among
+  if ((int64_t)batch * a->heads * nqb > 2 * (int64_t)h->sm_count && nqb < 13) return false;
+  if ((int64_t)batch * (a->heads / a->group) > krea_cuda::kKeyCounters) return false;
+  if (key_slice_rows(a->Lq, a->Lk) > 2048) return false;          // few queries, many keys: the separate pass is faster
+  if (a->text_len && a->text_slots >= a->Lk) return false;        // every work item must have keys to visit
+  return true;
+}
 
 static int run_attention(krea_cuda* h, const AttnCall& c) {
   if (c.Lq < 0 || c.Lk < 0 || c.heads < 0 || c.batch < 0) return fail(h, KREA_CUDA_E_ARG, "attention: negative size");
@@ -398,6 +437,23 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   p.wait_limit_ns = h->wait_limit_ns;
   p.test_drop_last_k = h->test_drop_last_k;
   p.pdl = c.pdl ? 1 : 0;
+  const bool persist = !partial && runs_persistent(h, c.batch, c.heads, c.Lq);
+  if (c.Kraw != nullptr) {
+    if (!persist) return fail(h, KREA_CUDA_E_ARG, "attention: K can only be normalised inside the persistent kernel");
+    p.Kraw = (const __nv_bfloat16*)c.Kraw;
+    p.ldkr = c.ldkr; p.bskr = c.bskr;
+    p.wk = c.wk;
+    p.Kn = (__nv_bfloat16*)const_cast<void*>(c.K);
+    uint32_t* counters = h->status_dev + 64;
+    p.kcount = counters + (h->kfuse_seq & 1) * krea_cuda::kKeyCounters;
+    p.kcount_clear = counters + ((h->kfuse_seq + 1) & 1) * krea_cuda::kKeyCounters;
+    p.kcount_clear_n = krea_cuda::kKeyCounters;
+    p.k_slices = attn_query_blocks(c.Lq);
+    p.k_slice_rows = key_slice_rows(c.Lq, c.Lk);
+    p.bound_in_kernel = h->static_bound ? 1 : 0;
+    p.logit_bound = nullptr;
+    p.pdl = 0;      // the kernel reads the caller's K: it must not start before the stream's previous kernel has ended
+  }
   if (c.o_blk != nullptr) {
     if (c.batch != 1 || c.o_blk_rows <= 0 || c.o_blk_n < 1 || c.o_blk_n > 8 || (int64_t)c.o_blk_n * c.o_blk_rows < c.Lq)
       return fail(h, KREA_CUDA_E_ARG, "attention: bad output row-block table");
@@ -433,14 +489,11 @@ static int run_attention(krea_cuda* h, const AttnCall& c) {
   }
   {
     ProfileMark pm(h, 1);
-    // One CTA per SM walking over its work items pays when there is more than one item per CTA; a problem that
-    // fits the SMs in one wave runs the one-item kernel (measured at 120 items: 4 % faster).
-    const long long items = (long long)((c.Lq + 255) / 256) * c.heads * c.batch;
-    const bool persist = h->persist != 0 && h->sm_count > 0 && !partial && (h->persist == 2 || items > h->sm_count);
     if (persist) CUDA_TRY(h, launch_attention_persist_sm100(tmK, tmV, tmQ, p, h->emu, h->sm_count, h->stream));
     else CUDA_TRY(h, launch_attention_sm100(tmK, tmV, tmO, tmQ, p, partial ? 1 : h->split, h->emu, h->stream));
   }
   h->launches++;
+  if (c.Kraw != nullptr) h->kfuse_seq++;
   return KREA_CUDA_OK;
 }
 
@@ -535,7 +588,7 @@ static int joint_prepass(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr
 }
 
 static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr, void* const* o_blk = nullptr, int o_blk_n = 0,
-                        int o_blk_rows = 0) {
+                        int o_blk_rows = 0, bool keys_inside = false) {
   const int batch = a->batch <= 0 ? 1 : a->batch;
   const int kvheads = a->heads / a->group;
   AttnCall c{};
@@ -549,10 +602,16 @@ static int joint_attend(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr,
   c.logit_bound = (float*)(h->status_dev + 8);
   c.o_blk = o_blk; c.o_blk_n = o_blk_n; c.o_blk_rows = o_blk_rows;
   c.pdl = h->pdl;          // the kernel right before this one in the stream is the K pre-pass
+  if (keys_inside) {
+    // no pre-pass: the attention kernel normalises the caller's K into the scratch itself (and works out the bound)
+    c.Kraw = a->K; c.ldkr = a->ldk; c.bskr = a->bsk; c.wk = a->wk;
+    c.logit_bound = nullptr;
+  }
   return run_attention(h, c);
 }
 
 static int joint_on_device(krea_cuda* h, const krea_cuda_joint_args* a, void* kscr) {
+  if (fuse_keys(h, a)) return joint_attend(h, a, kscr, nullptr, 0, 0, true);
   const int rc = joint_prepass(h, a, kscr);
   return rc ? rc : joint_attend(h, a, kscr);
 }

@@ -538,11 +538,15 @@ def test_sequence_parallel_entry_points_on_one_rank(kc):
                                  {"KREA_CUDA_PERSIST": "0", "KREA_CUDA_PDL": "0"}, {"KREA_CUDA_Q_TMA": "0"},
                                  {"KREA_CUDA_PERSIST": "2"}, {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_EMU": "1"},
                                  {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_STATIC_BOUND": "0"}, {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_PDL": "0"},
-                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_Q_TMA": "0"}])
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_Q_TMA": "0"},
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_KFUSE": "1"},
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_KFUSE": "1", "KREA_CUDA_STATIC_BOUND": "0"},
+                                 {"KREA_CUDA_PERSIST": "2", "KREA_CUDA_KFUSE": "1", "KREA_CUDA_EMU": "1"}])
 def test_tuning_knob_variants(monkeypatch, env):
     """The build-time variants a handle can select through its environment (the one-item-per-CTA kernel instead
     of the persistent one, two softmax threads per row, polynomial exp2 for a quarter of the elements, online max
-    instead of the a-priori bound, plain instead of programmatic launch, copy loop instead of TMA output stores)
+    instead of the a-priori bound, plain instead of programmatic launch, copy loop instead of TMA output stores, K
+    normalised inside the persistent kernel instead of by a kernel of its own)
     give the same results within tolerance, including a ragged key tail, GQA and the padding mask."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
@@ -558,6 +562,42 @@ def test_tuning_knob_variants(monkeypatch, env):
         check(got, want, None, f"variant {env}")
     finally:
         k2.close()
+
+
+@pytest.mark.parametrize("group,mode,masked", [(1, 0, False), (2, 1, True), (1, 2, False)])
+def test_keys_normalised_inside_the_kernel_give_the_same_bits(monkeypatch, group, mode, masked):
+    """The fused call's option to normalise K inside the persistent attention kernel (every work item does a
+    slice of its head's key rows, counters tell the TMA producers when a head's keys are complete) against the
+    default, a K kernel of its own: one launch instead of two and the same output bits - at a size where a CTA
+    walks over three items, so that all three places that normalise slices (before the roles split, the staging
+    warpgroup, the two spare warps) take part; with GQA, every RoPE mode and the padding mask."""
+    B, H, T, gh, gw = 1, 24, 136, 48, 68
+    S = T + gh * gw                                   # 3400 rows: 14 query blocks x 24 heads = 336 items on 148 CTAs
+    qkv, wq, wk, cos, sin = rand_case(404 + mode, B, S, H, T, gh, gw, group=group)
+    tl = np.array([77], dtype=np.int32) if masked else None
+    outs, launches = [], []
+    for fused in ("0", "1"):
+        monkeypatch.setenv("KREA_CUDA_KFUSE", fused)
+        k2 = ops.KreaCuda(0)
+        try:
+            k2.set_stream(torch.cuda.current_stream())
+            for _ in range(2):                        # twice: the second launch counts in the other set of counters
+                n0 = k2.launches
+                got = run_joint(k2, qkv, B, S, H, wq, wk, cos, sin, group=group, text_len=tl, text_slots=T if masked else 0, rope_mode=mode)
+                launches.append(k2.launches - n0)
+                outs.append(got)
+        finally:
+            k2.close()
+    assert launches == [2, 2, 1, 1]
+    assert np.isfinite(outs[0]).all()
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    # ... and those bits are right: some rows of the first and the last head against the oracle
+    rows = np.array([0, 1, 76, 77, 135, 136, 1700, 3071, 3072, 3399], dtype=np.int32)
+    for h in (0, H - 1):
+        want = oracle.joint_attention_rows(qkv[0], S, H, h, wq, wk, cos, sin, rows, rope_mode=mode, text_len=77 if masked else -1,
+                                           text_slots=T if masked else 0, group=group)
+        check(outs[2].reshape(S, H, 128)[rows, h], want, None, f"keys normalised inside the kernel, head {h}")
 
 
 def test_profile_marks_and_trace_file(kc, tmp_path):

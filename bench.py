@@ -572,7 +572,7 @@ def run_kernel_workload(args, rank, world, local_rank):
                   "l2": "two rotating operand sets (387 MB each > 126 MB L2)", "flops_per_step_per_gpu": work}
         extra = {"plain_store_tflops": work / ms_plain / 1e9, "library_gemm_tflops": work / ms_lib / 1e9,
                  "library_gemm": "torch.matmul (cuBLAS), same process, same operands"}
-        kernel, traffic = "gemm_bf16_sm100<256>", None
+        kernel, traffic = "gemm_bf16_sm100<256, cta pair>", None
     else:
         T, H = 4096, 20
         rows, ld = T * 12, 4 * H * 128

@@ -200,9 +200,11 @@ struct GemmParams {
   float* qbig;
   float* kbig;
   uint32_t* status;
+  int group_m;                  // set by the launcher: row blocks per group of the tile order
 };
 // A: 3-D map (k, row, 1) with 64 x 128 boxes; Wt: (n, k, 1) with 64 x 64 boxes; both 128-byte swizzled.
-// force_bn: 0 = choose the tile width (256 or 128 columns) by how well the tiles fill the last wave; 128 / 256 = as told
+// force_bn: 0 = choose the tile (128 x 128, 128 x 256, or 256 x 256 on a CTA pair) by how well the tiles fill the
+// last wave; 128 / 256 = one-CTA tile of that width, 512 = the CTA-pair tile
 // tmA2 / tmW2 describe the second product the same way (ignored when p.K2 == 0)
 cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
                                    int sms, int force_bn, cudaStream_t stream);

@@ -14,12 +14,20 @@
 //     drain the other accumulator - the epilogue of tile i overlaps the main loop of tile i + 1;
 //   * a thread of the epilogue owns one output row (= one TMEM lane), so a head's 128 columns - its sum of
 //     squares, its rotation pairs - are all in that thread's registers: the fused norm needs no exchange;
-//   * every wait is bounded (status word, normal exit) as in the attention kernel.
+//   * every wait is bounded (status word, normal exit) as in the attention kernel;
+//   * PAIR: the same kernel on clusters of two CTAs (tcgen05 cta_group::2): a pair works on a 256 x 256 tile, each
+//     CTA loads its own 128 rows of A and HALF of the Wt tile (128 columns) - 32 KB instead of 48 KB into shared
+//     memory per 512 tensor-pipe clocks - the leader CTA's MMA warp issues M256 N256 K16 products that read both
+//     CTAs' shared memory and write both CTAs' tensor memory, and every CTA drains its own 128 accumulator rows.
+//     All loads signal the leader's barriers; stage releases and accumulator hand-overs are committed to both
+//     CTAs (two plain commits, no multicast anywhere).  Measured at 4608 x 9216 x 3072: 1503-1534 TFLOP/s against
+//     1402-1434 for the one-CTA tile and 1505 for the library GEMM on the same box.
 #include <mutex>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "attention_sm100.h"
 #include "sm100_ptx.cuh"
@@ -34,35 +42,84 @@ constexpr int THREADS = 256;                  // warp 0 TMA, warp 1 MMA, warps 4
 enum : uint32_t { SITE_FULL = 11, SITE_EMPTY = 12, SITE_ACC_FULL = 13, SITE_ACC_EMPTY = 14 };
 // Tile width: 256 columns halve the A traffic per flop; 128 columns give twice as many tiles, which only pays
 // when the 256-wide tiles would leave most of the 148 CTAs idle (small problems).
-template <int BN_>
+// ---- the CTA-pair forms of the instructions (cluster of two CTAs, rank 0 = leader) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load into this CTA's shared memory; the bytes are counted on an mbarrier that may sit in the peer CTA
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const void* tmap, uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ss2(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+// one arrival on the mbarrier at this shared::cluster address once every MMA issued so far has finished
+__device__ __forceinline__ void umma_commit2(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <int BN_, bool PAIR_ = false>
 struct Cfg {
   static constexpr int BN = BN_;
-  static constexpr int B_BYTES = BK * BN * 2;                 // BN / 64 blocks
+  static constexpr int BN_CTA = PAIR_ ? BN / 2 : BN;          // columns of Wt this CTA stages
+  static constexpr int B_BYTES = BK * BN_CTA * 2;             // BN_CTA / 64 blocks
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KB or 32 KB
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int STAGES = STAGE_BYTES == 48 * 1024 ? 4 : 6;
   static constexpr int SMEM = STAGES * STAGE_BYTES + 256 + 1024;
 };
 }  // namespace gemm
 
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA2,
                 const __grid_constant__ CUtensorMap tmW2, const GemmParams p) {
   using namespace gemm;
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;             // rows of an output tile (of the pair's)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
-  uint64_t* full = bars;                 // [STAGES] TMA landed
+  uint64_t* full = bars;                 // [STAGES] TMA landed (PAIR: the leader's count both CTAs' bytes)
   uint64_t* empty = bars + STAGES;       // [STAGES] MMAs that read the stage have finished
   uint64_t* acc_full = empty + STAGES;   // [2] accumulator complete
-  uint64_t* acc_empty = acc_full + 2;    // [2] accumulator drained by the epilogue warps
+  uint64_t* acc_empty = acc_full + 2;    // [2] accumulator drained by the epilogue warps (PAIR: the leader's, by both CTAs')
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile uint32_t* abort_word = (volatile uint32_t*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = (p.M + BM - 1) / BM, nt = (p.N + BN - 1) / BN;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;     // 0 = leader
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int mt = (p.M + TILE_M - 1) / TILE_M, nt = (p.N + BN - 1) / BN;
   // the optional second product (A2 x W2, the reference's LoRA term, gemm.metal:46-50) is just more k-blocks
   // accumulated into the same tile before the epilogue
   const int kb1 = (p.K + BK - 1) / BK, kblocks = kb1 + (p.K2 + BK - 1) / BK;
@@ -75,31 +132,37 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 128);
+      mbar_init(&acc_empty[a], PAIR ? 256 : 128);
     }
     abort_word[0] = (p.status != nullptr && *p.status != 0u) ? 0xFFu : 0u;
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc2(tmem_slot, 2 * BN);      // one warp of each CTA of the pair
+      tmem_relinquish2();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised, both allocations are done
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   // tile t -> (m tile, n tile): tiles are dealt out in groups of GROUP_M row blocks x all column blocks, row
-  // block fastest inside a group.  The CTAs running together then share ~16 row blocks of A and ~9 column
-  // blocks of Wt, a group's slice of A (a few MB) stays in L2 for the whole group, and with many row blocks A is
-  // not streamed through L2 once per column block.
-  constexpr int GROUP_M = 16;
+  // block fastest inside a group.  The CTAs running together then share GROUP_M row blocks of A and a few column
+  // blocks of Wt; the host sizes the group so that its slice of A (tens of MB at most) stays in L2 while the group
+  // sweeps the columns: Wt is then streamed from HBM once per group and A once.
+  const int GROUP_M = p.group_m;
   auto tile_origin = [&](int t, int& m0, int& n0) {
     const int per_group = GROUP_M * nt;
     const int g = t / per_group, first = g * GROUP_M;
     const int gm = min(GROUP_M, mt - first);
     const int local = t - g * per_group;
-    m0 = (first + local % gm) * BM;
+    m0 = (first + local % gm) * TILE_M + (int)rank * BM;      // this CTA's rows of the tile
     n0 = (local / gm) * BN;
   };
   if (warp == 0) {
@@ -112,7 +175,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tma_prefetch_desc(&tmW2);
       }
       uint32_t n = 0;     // k-blocks issued so far
-      for (int t = blockIdx.x; t < tiles && *abort_word == 0u; t += gridDim.x) {
+      for (int t = worker; t < tiles && *abort_word == 0u; t += workers) {
         int m0, n0;
         tile_origin(t, m0, n0);
         for (int kb = 0; kb < kblocks; kb++, n++) {
@@ -120,32 +183,44 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (!mbar_wait(&empty[s], ((n / STAGES) & 1) ^ 1, abort_word, SITE_EMPTY)) break;
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_BYTES;
-          mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
           const CUtensorMap* ma = kb < kb1 ? &tmA : &tmA2;
           const CUtensorMap* mw = kb < kb1 ? &tmW : &tmW2;
           const int k0 = (kb < kb1 ? kb : kb - kb1) * BK;
-          tma_load_3d(a_dst, ma, &full[s], k0, m0, 0);
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier, which the leader arms for both
+            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * STAGE_BYTES);
+            const uint32_t bar = mapa(smem_u32(&full[s]), 0);
+            tma_load_3d_pair(a_dst, ma, bar, k0, m0, 0);
 #pragma unroll
-          for (int j = 0; j < BN / 64; j++) tma_load_3d(b_dst + j * B_BLOCK, mw, &full[s], n0 + j * 64, k0, 0);
+            for (int j = 0; j < C::BN_CTA / 64; j++)
+              tma_load_3d_pair(b_dst + j * B_BLOCK, mw, bar, n0 + (int)rank * C::BN_CTA + j * 64, k0, 0);
+          } else {
+            mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+            tma_load_3d(a_dst, ma, &full[s], k0, m0, 0);
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++) tma_load_3d(b_dst + j * B_BLOCK, mw, &full[s], n0 + j * 64, k0, 0);
+          }
         }
       }
       // nothing may still be in flight into this CTA's shared memory when it exits
-      if (*abort_word != 0u) {
+      if (*abort_word != 0u && (!PAIR || rank == 0)) {
         for (uint32_t i = (n > STAGES ? n - STAGES : 0); i < n; i++)
           mbar_wait_slow(&full[i % STAGES], (i / STAGES) & 1, abort_word + 1, SITE_FULL);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 && rank == 0) {
     // ======================================== MMA issuer ========================================
+    // (PAIR: the leader CTA's only; A rows 0-127 and Wt columns 0-127 of a product come from its shared memory, the
+    // others from the same offsets of the peer's; accumulator rows 128-255 live in the peer's tensor memory)
     const bool leader = elect_one();
-    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, true);
+    constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN, true);
     constexpr uint32_t HI = desc_hi(1024);
     constexpr uint32_t LBO_A = (16u >> 4) << 16;                       // K-major: unused
     constexpr uint32_t LBO_B = ((uint32_t)B_BLOCK >> 4) << 16;         // N-major: next 64 columns 8 KB away
     const uint32_t smem_lo = smem_u32(smem) >> 4;
     uint32_t n = 0;
     int it = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+    for (int t = worker; t < tiles; t += workers, it++) {
       const int a = it & 1;
       if (it >= 2) {
         if (!mbar_wait(&acc_empty[a], ((it >> 1) - 1) & 1, abort_word, SITE_ACC_EMPTY)) break;
@@ -162,14 +237,33 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int k = 0; k < BK / 16; k++) {
           const uint64_t da = make_desc(a_lo + k * 2, HI), db = make_desc(b_lo + k * 128, HI);   // 32 B / 2048 B per 16 k
           if (leader) {
-            if (kb == 0 && k == 0) umma_ss<false>(d_tmem, da, db, idesc);
-            else umma_ss<true>(d_tmem, da, db, idesc);
+            if constexpr (PAIR) {
+              if (kb == 0 && k == 0) umma_ss2<false>(d_tmem, da, db, idesc);
+              else umma_ss2<true>(d_tmem, da, db, idesc);
+            } else {
+              if (kb == 0 && k == 0) umma_ss<false>(d_tmem, da, db, idesc);
+              else umma_ss<true>(d_tmem, da, db, idesc);
+            }
           }
         }
-        if (leader) umma_commit(&empty[s]);
+        if (leader) {
+          if constexpr (PAIR) {
+            umma_commit2(mapa(smem_u32(&empty[s]), 0));
+            umma_commit2(mapa(smem_u32(&empty[s]), 1));
+          } else {
+            umma_commit(&empty[s]);
+          }
+        }
         __syncwarp();
       }
-      if (leader) umma_commit(&acc_full[a]);
+      if (leader) {
+        if constexpr (PAIR) {
+          umma_commit2(mapa(smem_u32(&acc_full[a]), 0));
+          umma_commit2(mapa(smem_u32(&acc_full[a]), 1));
+        } else {
+          umma_commit(&acc_full[a]);
+        }
+      }
       __syncwarp();
       if (*abort_word != 0u) break;
     }
@@ -191,7 +285,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int r = (warp & 3) * 32 + lane;                 // row of the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     int it = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, it++) {
+    for (int t = worker; t < tiles; t += workers, it++) {
       const int a = it & 1;
       int m0, n0;
       tile_origin(t, m0, n0);
@@ -238,6 +332,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           tmem_wait_ld();
           if (row < p.M) {
             const int ocol0 = (col0 >> 6) * 32;
+            uint32_t pk[16];
 #pragma unroll
             for (int q4 = 0; q4 < 4; q4++) {
               float f[8];
@@ -246,7 +341,15 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const float gv = __uint_as_float(g[q4 * 8 + e]);
                 f[e] = gv * sigmoid_approx(gv) * __uint_as_float(u[q4 * 8 + e]);      // common.h silu
               }
-              *(uint4*)(crow + ocol0 + q4 * 8) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+#pragma unroll
+              for (int e = 0; e < 4; e++) pk[q4 * 4 + e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+            }
+            if ((((uintptr_t)(crow + ocol0)) & 31u) == 0) {     // whole 32-byte sectors per store when the row allows it
+              st_global_32B(crow + ocol0, pk);
+              st_global_32B(crow + ocol0 + 16, pk + 8);
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; q4++) *(uint4*)(crow + ocol0 + q4 * 8) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
             }
           }
         }
@@ -356,7 +459,15 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               else p.kbig[(size_t)row * p.n_k + head] = v;
             }
           }
-          if (row < p.M) {
+          // 64 contiguous bytes of the row: two stores of a whole 32-byte sector each when the row allows it (a
+          // 16-byte store to 32 different rows fills every sector in two halves)
+          if (row < p.M && p.seg <= 0 && col0 + c0 + 32 <= p.N && (((uintptr_t)(crow + col0 + c0)) & 31u) == 0) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; e++) pk[e] = pack_bf16x2(f[2 * e], f[2 * e + 1]);
+            st_global_32B(crow + col0 + c0, pk);
+            st_global_32B(crow + col0 + c0 + 16, pk + 8);
+          } else if (row < p.M) {
 #pragma unroll
             for (int q4 = 0; q4 < 4; q4++) {
               const int col = col0 + c0 + q4 * 8;
@@ -371,15 +482,20 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(&acc_empty[a]);
+      if constexpr (PAIR) mbar_arrive_cluster(mapa(smem_u32(&acc_empty[a]), 0));   // the leader's barrier counts both CTAs' threads
+      else mbar_arrive(&acc_empty[a]);
     }
   }
 
+  // (PAIR) nobody leaves or frees tensor memory while the peer may still read this CTA's shared memory, signal its
+  // barriers or write its accumulator
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if constexpr (PAIR) tmem_dealloc2(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
   if (threadIdx.x == 0 && p.status != nullptr) {
     const uint32_t a = *abort_word;
@@ -387,8 +503,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
-template <int BN>
-static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
+template <int BN, bool PAIR>
+static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, GemmParams p,
                                        int sms, cudaStream_t stream) {
   using namespace gemm;
   static bool configured[64] = {};
@@ -398,15 +514,44 @@ static cudaError_t launch_gemm_variant(const CUtensorMap& tmA, const CUtensorMap
   {
     std::lock_guard<std::mutex> lock(configure_mutex);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM);
+      cudaError_t e = cudaFuncSetAttribute(gemm_bf16_sm100<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, PAIR>::SMEM);
       if (e != cudaSuccess) return e;
       configured[dev] = true;
     }
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
-  gemm_bf16_sm100<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(tmA, tmW, tmA2, tmW2, p);
-  return cudaGetLastError();
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;
+  const int tiles = ((p.M + TILE_M - 1) / TILE_M) * ((p.N + BN - 1) / BN);
+  // as many workers (CTAs, or CTA pairs) as the waves need: 1080 tiles on 74 pairs take 15 waves, and so they do on 72
+  // pairs, with four SMs' worth of power left to the others' clocks
+  int workers = PAIR ? sms / 2 : sms;
+  if (tiles < workers) workers = tiles;
+  const int waves = (tiles + workers - 1) / workers;
+  workers = (tiles + waves - 1) / waves;
+  const int grid = workers * (PAIR ? 2 : 1);
+  // row blocks per group: the group's slice of A (rows x K, 32 MB at most) should stay in L2 while the group sweeps
+  // the columns; groups of equal size (measured at 4608 x 15360 x 6144: groups of 8-9 row blocks of 256 rows 1512-1528
+  // TFLOP/s, of 4: 1468, of 18: 1490; at K = 3072 all 18 in one group 1511, two groups of 16 + 2: 1494)
+  const long long k_all = (long long)p.K + p.K2;
+  const int mt = (p.M + TILE_M - 1) / TILE_M;
+  long long gmax = (32ll << 20) / (k_all * 2 * TILE_M);
+  if (gmax < 1) gmax = 1;
+  const int groups = (int)((mt + gmax - 1) / gmax);
+  p.group_m = (mt + groups - 1) / groups;
+  static const int group_m_knob = [] { const char* e = getenv("KREA_CUDA_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();   // tuning knob
+  if (group_m_knob > 0) p.group_m = group_m_knob;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = Cfg<BN, PAIR>::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PAIR ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, gemm_bf16_sm100<BN, PAIR>, tmA, tmW, tmA2, tmW2, (const GemmParams)p);
 }
 
 cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmA2, const CUtensorMap& tmW2, const GemmParams& p,
@@ -421,8 +566,15 @@ cudaError_t launch_gemm_bf16_sm100(const CUtensorMap& tmA, const CUtensorMap& tm
   };
   // the narrow tile moves a third more bytes through shared memory per flop and measures ~20 % slower per tile
   // (1100 against 1340 TFLOP/s on full waves), so it has to fill the waves a good deal better to win
-  const bool narrow = force_bn == 128 || (force_bn != 256 && wave_eff(128) > wave_eff(256) * 1.3);
-  return narrow ? launch_gemm_variant<128>(tmA, tmW, tmA2, tmW2, p, sms, stream) : launch_gemm_variant<256>(tmA, tmW, tmA2, tmW2, p, sms, stream);
+  const bool narrow = force_bn == 128 || (force_bn == 0 && wave_eff(128) > wave_eff(256) * 1.3);
+  if (narrow) return launch_gemm_variant<128, false>(tmA, tmW, tmA2, tmW2, p, sms, stream);
+  // 256 x 256 tiles on CTA pairs: 7 % faster per tile (a third fewer bytes into shared memory), with half as many,
+  // twice as large units of work to fill the last wave with
+  const int pairs = sms / 2;
+  const long long ptiles = (long long)((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + 255) / 256);
+  const double pair_eff = pairs > 0 ? (double)ptiles / (double)(((ptiles + pairs - 1) / pairs) * pairs) : 0.0;
+  const bool pair = pairs > 0 && (force_bn == 512 || (force_bn == 0 && pair_eff * 1.07 >= wave_eff(256)));
+  return pair ? launch_gemm_variant<256, true>(tmA, tmW, tmA2, tmW2, p, sms, stream) : launch_gemm_variant<256, false>(tmA, tmW, tmA2, tmW2, p, sms, stream);
 }
 
 }  // namespace krea

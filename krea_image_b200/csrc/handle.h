@@ -53,7 +53,8 @@ struct krea_cuda {
   std::vector<cudaEvent_t> event_pool;
   cudaEvent_t trace_base = nullptr;   // recorded by krea_cuda_profile_enable(h, 1): time zero of the trace file
   KreaDist* dist = nullptr;         // set by krea_cuda_dist_init
-  int gemm_bn = 0;                  // GEMM tile width: 0 = chosen per problem, 128 or 256 = forced
+  int gemm_bn = 0;                  // GEMM tile: 0 = chosen per problem; 128 or 256 = one-CTA tile of that width,
+                                    // 512 = 256 x 256 tile on a CTA pair
   int sm_count = 0;                 // SMs of the device (persistent kernels size their grid by it)
   void* block_ws = nullptr;         // intermediates of krea_cuda_dit_block when the caller passes no workspace
   size_t block_ws_bytes = 0;

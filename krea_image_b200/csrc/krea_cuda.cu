@@ -117,7 +117,7 @@ krea_cuda* krea_cuda_create(int device, char* err, int errlen) {
   if (const char* s = getenv("KREA_CUDA_Q_TMA")) h->q_tma = atoi(s) != 0;                 // tuning knob
   if (const char* s = getenv("KREA_CUDA_GEMM_BN")) {                                      // tuning knob: GEMM tile width
     const int v = atoi(s);
-    if (v == 128 || v == 256) h->gemm_bn = v;
+    if (v == 128 || v == 256 || v == 512) h->gemm_bn = v;     // 512: 256 x 256 tiles on CTA pairs
   }
   if (const char* s = getenv("KREA_CUDA_EMU")) {  // tuning knob: share of exp2 evaluated on the FMA pipe (0-3 of 4)
     const int v = atoi(s);

@@ -11,9 +11,18 @@ from oracle import oracle_np
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def kc():
-    k = ops.KreaCuda(0)
+@pytest.fixture(scope="module", params=["by-size", "cta-pair"])
+def kc(request):
+    """Every test of this module runs twice: with the library choosing the tile by problem size (small cases take
+    the one-CTA tiles) and with the 256 x 256 tile on CTA pairs forced, so that its loads, products and every
+    epilogue see the same ragged shapes."""
+    import os
+    if request.param == "cta-pair":
+        os.environ["KREA_CUDA_GEMM_BN"] = "512"
+    try:
+        k = ops.KreaCuda(0)
+    finally:
+        os.environ.pop("KREA_CUDA_GEMM_BN", None)
     k.set_stream(torch.cuda.current_stream())
     yield k
     k.close()
@@ -140,12 +149,12 @@ def test_gemm_swiglu_epilogue(kc):
 
 
 def test_gemm_tile_width_variants(monkeypatch):
-    """The two tile widths (128 x 256 and 128 x 128, chosen per problem by how the tiles fill the CTAs' last wave)
-    accumulate every output element in the same order: forced either way, the results are bit-identical."""
+    """The three tiles (128 x 256, 128 x 128 and 256 x 256 on a CTA pair, chosen per problem by how the tiles fill
+    the last wave) accumulate every output element in the same order: forced any way, the results are bit-identical."""
     M, N, K = 300, 1000, 328
     a, w = _case(41, M, N, K, K, N)
     outs = []
-    for bn in ("128", "256"):
+    for bn in ("128", "256", "512"):
         monkeypatch.setenv("KREA_CUDA_GEMM_BN", bn)
         k2 = ops.KreaCuda(0)
         try:
@@ -156,7 +165,7 @@ def test_gemm_tile_width_variants(monkeypatch):
             outs.append(c)
         finally:
             k2.close()
-    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     want = synth.bf16_bits_to_f32(a).astype(np.float64) @ synth.bf16_bits_to_f32(w).astype(np.float64)
     rel, _ = _rel(outs[0].float().cpu().numpy(), want)
     assert rel <= 3e-3

@@ -48,8 +48,8 @@ METRIC = "joint-attn TFLOP/s at S=4608 (1024^2), 24 heads, head_dim 128"
 FALLBACK_PEAK_TFLOPS = 1590.0
 WORKLOADS = {"c0": 0, "c1": 1, "c2": 2, "c3": 3, "c4": 4}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch at config 1, from one ncu capture of
-# this workload: 87.5 MB read + 8.8 MB written (algorithmic 113.2 MB; the output stays in L2)
-ATTN_DRAM_TRAFFIC_BYTES = {1: 96.3e6}
+# this workload: 87.8 MB read + 11.0 MB written (algorithmic 113.2 MB; most of the output is still in L2 at the end)
+ATTN_DRAM_TRAFFIC_BYTES = {1: 98.8e6}
 REPEATS = 9          # timed batches of `steps` steps each; the reported time per step is the median batch
 PARITY_REL_L2, PARITY_MAX_ABS = 5e-3, 2e-2
 

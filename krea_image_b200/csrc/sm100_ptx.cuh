@@ -1,6 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features the attention kernel is built from:
 // mbarriers with BOUNDED waits, TMA tile loads, tcgen05 tensor-core MMAs, and tensor-memory (TMEM)
-// allocation / loads / stores.  Everything is cta_group::1 and cluster size 1; no multicast anywhere.
+// allocation / loads / stores.  Everything here is cta_group::1 and cluster size 1 (the CTA-pair forms live with
+// their only user, gemm_sm100.cu); no multicast anywhere.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -1,5 +1,5 @@
 /* Plain-C consumer of include/krea_cuda.h: the header must compile as C11 and the library must link and answer
- * from C, the way the reference's own C ABI (engine/include/krea.h) is consumed.  Needs no GPU: without one,
+ * from C, the way the reference's own C ABI (engine/src/krea.h) is consumed.  Needs no GPU: without one,
  * krea_cuda_create must fail with a message, and the host-side entry points must still work. */
 #include <math.h>
 #include <stdio.h>

@@ -752,8 +752,15 @@ def run_ours(args, rank, world, local_rank):
     if cfg.cid == 1 and not by_heads and not args.no_multi:
         del xs, os_
         torch.cuda.empty_cache()
-        multi = {"head_split_c3": measure_head_split(kc, 3, max(3, min(args.steps, 10)), 3, 3, ranks, stream),
-                 "seqpar_c4": measure_seq_parallel(kc, max(2, min(args.steps, 5)), 2, 3, ranks, stream, args.a2a),
+        # A failure here (say, no room for the long sequence beside another job) must not take the headline with
+        # it: the line then carries the error text in place of the numbers.
+        def guarded(fn, *a):
+            try:
+                return fn(*a)
+            except Exception as e:      # noqa: BLE001 - reported, not hidden
+                return {"error": f"{type(e).__name__}: {e}"[:400]}
+        multi = {"head_split_c3": guarded(measure_head_split, kc, 3, max(3, min(args.steps, 10)), 3, 3, ranks, stream),
+                 "seqpar_c4": guarded(measure_seq_parallel, kc, max(2, min(args.steps, 5)), 2, 3, ranks, stream, args.a2a),
                  "note": "strong scaling: one problem over all GPUs; efficiency = ms_per_step(1 GPU) / (N * ms_per_step(N GPUs))"}
 
     if rank == 0:
